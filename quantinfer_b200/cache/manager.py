@@ -36,7 +36,9 @@ import numpy as np
 import torch
 
 from ..errors import CacheError, OutOfPages
-from .needs import PagedKVNeed, StateNeed
+from .needs import PagedKVNeed, PagedLatentNeed, StateNeed
+
+_PAGED = (PagedKVNeed, PagedLatentNeed)
 
 
 class PageAllocator:
@@ -69,11 +71,11 @@ class PageAllocator:
 
 @dataclass
 class Group:
-    need: PagedKVNeed
+    need: object             # PagedKVNeed or PagedLatentNeed
     entries: list            # cache entry indices, in pool order
     allocator: PageAllocator
-    k: Optional[torch.Tensor] = None   # [entries, num_pages, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    k: Optional[torch.Tensor] = None   # [entries, num_pages, *page shape]: kv_heads, page_size, head_dim, or page_size, width
+    v: Optional[torch.Tensor] = None   # None for a need with one pool
 
 
 @dataclass
@@ -118,9 +120,9 @@ class CacheManager:
         self._entry_group: dict[int, tuple] = {}     # entry -> (group index, index in group)
         self.states: dict[int, torch.Tensor] = {}    # entry -> [num_slots, *shape]
         self._state_saved: dict[int, torch.Tensor] = {}   # the rows as they were before the step in flight
-        by_need: dict[PagedKVNeed, int] = {}
+        by_need: dict = {}
         for entry, need in enumerate(self.needs):
-            if isinstance(need, PagedKVNeed):
+            if isinstance(need, _PAGED):
                 if need not in by_need:
                     by_need[need] = len(self.groups)
                     self.groups.append(Group(need, [], PageAllocator(num_pages)))
@@ -136,9 +138,9 @@ class CacheManager:
                 raise CacheError(f"cache entry {entry} asks for {need!r}, which the manager does not know")
         if self.device is not None:
             for g in self.groups:
-                shape = (len(g.entries), num_pages, g.need.num_kv_heads, page_size, g.need.head_dim)
-                g.k = torch.zeros(shape, dtype=dtype, device=self.device)
-                g.v = torch.zeros(shape, dtype=dtype, device=self.device)
+                k_page, v_page = g.need.pools(page_size)
+                g.k = torch.zeros((len(g.entries), num_pages, *k_page), dtype=dtype, device=self.device)
+                g.v = torch.zeros((len(g.entries), num_pages, *v_page), dtype=dtype, device=self.device) if v_page else None
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.requests: dict[object, RequestCache] = {}
         # block tables by slot, kept as arrays so that a batch's tables are one gather
@@ -149,8 +151,12 @@ class CacheManager:
     def pool_bytes(self) -> int:
         total = 0
         for g in self.groups:
-            n = len(g.entries) * self.num_pages * g.need.num_kv_heads * self.page_size * g.need.head_dim
-            total += 2 * n * torch.empty((), dtype=self.dtype).element_size()
+            for page in g.need.pools(self.page_size):
+                if page:
+                    n = len(g.entries) * self.num_pages
+                    for s in page:
+                        n *= s
+                    total += n * torch.empty((), dtype=self.dtype).element_size()
         return total
 
     def free_pages(self, group: int = 0) -> int:
@@ -272,7 +278,7 @@ class CacheManager:
 
     def view(self, entry: int, writes: bool = True) -> CacheView:
         need = self.needs[entry]
-        if isinstance(need, PagedKVNeed):
+        if isinstance(need, _PAGED):
             g, idx = self._entry_group[entry]
             grp = self.groups[g]
             return CacheView(entry, g, self.page_size,

@@ -187,6 +187,8 @@ def generate(arguments) -> int:
     if eos is not None and eos >= spec.vocab_size:
         raise UsageError("EOS token id is outside the model vocabulary")
     max_sequence_length = max_seq if max_seq is not None else spec.max_positions
+    if max_seq is None and spec.max_positions >= 1 << 30:      # a design without a limit: as long as this call needs
+        max_sequence_length = max(len(p) for p in prompts) + max_new
     if max_sequence_length == 0 or max_sequence_length > spec.max_positions:
         raise UsageError(f"--max-sequence-length must be between 1 and {spec.max_positions}")
     longest = max(len(p) for p in prompts)

@@ -1,11 +1,14 @@
 from .qwen3 import Qwen3Config
 from .registry import (architectures, config_class_for, config_from_dict, load_config,
                        register_architecture)
-from .spec import (AttentionSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec, LayerCall, LayerSpec,
-                   ModelSpec, NormSpec, PositionSpec)
+from .bebuvik import BebuvikConfig
+from .spec import (AttentionSpec, BigramEmbeddingSpec, DenseFeedForwardSpec, EmbeddingSpec, FeedForwardSpec, HeadSpec,
+                   LatentAttentionSpec, LayerCall, LayerSpec, ModelSpec, NormSpec, ParallelLayerSpec, PositionSpec,
+                   RotarySpec, ShortConvSpec)
 
 __all__ = [
     "Qwen3Config", "architectures", "config_class_for", "config_from_dict", "load_config",
     "register_architecture", "AttentionSpec", "EmbeddingSpec", "FeedForwardSpec", "HeadSpec",
-    "LayerCall", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec",
+    "LayerCall", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec", "BebuvikConfig", "BigramEmbeddingSpec",
+    "DenseFeedForwardSpec", "LatentAttentionSpec", "ParallelLayerSpec", "RotarySpec", "ShortConvSpec",
 ]

@@ -56,8 +56,10 @@ def config_from_dict(d: dict):
     if not isinstance(d, dict):
         raise ConfigError("config.json must hold a JSON object")
     arch = d.get("architectures")
+    if arch is None and isinstance(d.get("architecture"), str):
+        arch = [d["architecture"]]          # some designs name themselves with one string
     if not isinstance(arch, list) or not arch or not isinstance(arch[0], str):
-        raise ConfigError("config.json must name the model class under `architectures`")
+        raise ConfigError("config.json must name the model class under `architectures` (or `architecture`)")
     for name in arch:
         if name in _ARCHITECTURES:
             return _ARCHITECTURES[name].from_dict(d)
@@ -68,6 +70,9 @@ def _register_builtin() -> None:
     from .qwen3 import ARCHITECTURE, Qwen3Config
 
     register_architecture(ARCHITECTURE, Qwen3Config)
+    from .bebuvik import ARCHITECTURE as BEBUVIK, BebuvikConfig
+
+    register_architecture(BEBUVIK, BebuvikConfig)
 
 
 _register_builtin()

@@ -21,6 +21,9 @@ from typing import Optional
 
 @dataclass(frozen=True)
 class NormSpec:
+    """`kind` "rmsnorm": gain per coordinate, tensor `prefix + "weight"`. "rmsnorm_scalar": one gain for all
+    coordinates, the tensor named `prefix` itself, of shape []."""
+
     size: int
     eps: float
     prefix: str = ""
@@ -70,6 +73,102 @@ class FeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class RotarySpec:
+    """Rotary encoding whose angles are computed where they are used (no table, so no limit on
+    positions): pair i of the first `rotary_dim` coordinates of a part turns by position *
+    theta^(-2i / rotary_dim). `pairing` as for :class:`PositionSpec`."""
+
+    rotary_dim: int
+    theta: float
+    pairing: str = "interleaved"
+    kind: str = "rope_direct"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention over a cached low-rank latent: a position caches `kv_rank` numbers (normalised,
+    gain per coordinate) and a rotated key part of `rot_dim` numbers that all heads share; per head the
+    key's plain part (`head_dim` numbers) and the value (`value_dim`) are projections of the latent.
+    `shares_latent`: the layer has no latent projection and reads the cache entry of another layer.
+    `sink`: the softmax's denominator holds one more learned term per head."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rot_dim: int
+    value_dim: int
+    kv_rank: int
+    position: Optional[RotarySpec]
+    norm_eps: float
+    scale: float
+    window: Optional[int] = None
+    sink: bool = False
+    shares_latent: bool = False
+    prefix: str = ""
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DenseFeedForwardSpec:
+    """Feed-forward without a gate: down(act(up(x)))."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "gelu_tanh"
+    prefix: str = ""
+    kind: str = "dense_mlp"
+
+
+@dataclass(frozen=True)
+class ShortConvSpec:
+    """A bank of short causal convolutions over time that read one input: filter k has `taps` weights per
+    channel, stored as the tensor `names[k]` of shape [width, taps]; out_k = (input if `residual`) +
+    filter_k(input). The last taps - 1 inputs are a request's state."""
+
+    width: int
+    taps: int
+    names: tuple
+    residual: bool = True
+    kind: str = "short_conv"
+
+
+@dataclass(frozen=True)
+class ParallelLayerSpec:
+    """One block with one norm whose output feeds the mixer and the feed-forward side by side:
+    h = norm(x); x += gate_m * mixer(conv_m(h)) + gate_f * ffn(conv_f(h)). `conv` (optional) is the bank
+    of input convolutions, one filter per sublayer; `gate_names` (optional) are the prefixes of the sigmoid
+    gates' projections of h, one per sublayer ("<name>" the matrix, "<name>.b" the bias). `ffn` may be None."""
+
+    norm: NormSpec
+    mixer: object
+    ffn: object
+    conv: Optional[ShortConvSpec] = None
+    gate_names: Optional[tuple] = None
+    kind: str = "parallel_gated"
+
+    # what the model reads of any layer spec
+    @property
+    def mixer_norm(self):
+        return self.norm
+
+
+@dataclass(frozen=True)
+class BigramEmbeddingSpec:
+    """Token embedding plus a row of a hashed bigram table [buckets + 1, hidden]: row (previous * mul_prev +
+    current * mul_cur) mod buckets, the last row for a sequence's first token."""
+
+    vocab_size: int
+    hidden_size: int
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    table_name: str = "embed"
+    bigram_name: str = "bigram"
+    prefix: str = ""
+    kind: str = "bigram_embedding"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: x += mixer(norm(x)); x += ffn(norm(x)) for kind `prenorm`."""
 
@@ -99,6 +198,7 @@ class EmbeddingSpec:
     hidden_size: int
     prefix: str = ""
     kind: str = "embedding"
+    weight_name: Optional[str] = None   # the tensor's full name when it is not prefix + "weight"
 
 
 @dataclass(frozen=True)
@@ -108,6 +208,8 @@ class HeadSpec:
     tied: bool              # True: the head is the embedding table
     prefix: str = ""
     kind: str = "lm_head"
+    softcap: Optional[float] = None     # c: logits = c * tanh(logits / c)
+    weight_name: Optional[str] = None   # the tensor's full name when it is not prefix + "weight"
 
 
 @dataclass(frozen=True)

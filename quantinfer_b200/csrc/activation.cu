@@ -67,3 +67,88 @@ extern "C" int qi_silu_mul(const void* gate_up, void* out, int dtype, int n_toke
                            int interleaved, cudaStream_t stream) {
     return qi_act_mul(gate_up, out, dtype, n_tokens, inter, interleaved, 0, stream);
 }
+
+// ---- an activation alone, a sum of gated sublayer outputs, and the soft cap of logits ------------
+
+namespace {
+
+template <typename T, int ACT>
+__global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
+    qi::pdl_enter();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = qi::from_f32<T>(act<ACT>(qi::to_f32<T>(in[idx])));
+}
+
+// out[t, c] = sigmoid(g[t, c] + b0[c]) * y0[t, c] (+ sigmoid(g[t, C + c] + b1[c]) * y1[t, c]), 32-bit out.
+template <typename TG, typename TY>
+__global__ void gated_sum_kernel(const TG* __restrict__ gates, int ldg, const float* __restrict__ b0,
+                                 const float* __restrict__ b1, const TY* __restrict__ y0, const TY* __restrict__ y1,
+                                 float* __restrict__ out, int n_tokens, int C) {
+    qi::pdl_enter();
+    const size_t total = (size_t)n_tokens * C;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / C, c = idx % C;
+        const TG* g = gates + t * ldg;
+        float v = qi::to_f32<TY>(y0[idx]) / (1.0f + expf(-(qi::to_f32<TG>(g[c]) + b0[c])));
+        if (y1) v += qi::to_f32<TY>(y1[idx]) / (1.0f + expf(-(qi::to_f32<TG>(g[C + c]) + b1[c])));
+        out[idx] = v;
+    }
+}
+
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
+    qi::pdl_enter();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] * inv_cap);
+}
+
+unsigned blocks_for(size_t total) {
+    size_t blocks = (total + 255) / 256;
+    return (unsigned)(blocks > 148 * 32 ? 148 * 32 : blocks);
+}
+
+}  // namespace
+
+// out = act(in), elementwise, both [n] in `dtype`; 32-bit arithmetic.
+extern "C" int qi_activation(const void* in, void* out, int dtype, long long n, int activation, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0, "activation: bad size");
+    QI_REQUIRE(activation >= 0 && activation <= 3, "activation: unknown activation code %d", activation);
+    if (n == 0) return 0;
+    const dim3 grid(blocks_for((size_t)n)), block(256);
+    QI_DISPATCH_DTYPE(dtype, T, {
+        switch (activation) {
+            case kSilu: qi::launch(activation_kernel<T, kSilu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+            case kGelu: qi::launch(activation_kernel<T, kGelu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+            case kGeluTanh: qi::launch(activation_kernel<T, kGeluTanh>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+            default: qi::launch(activation_kernel<T, kRelu>, grid, block, 0, stream, (const T*)in, (T*)out, (size_t)n); break;
+        }
+    });
+    return qi::check_launch("activation");
+}
+
+// The sum of one or two sublayer outputs, each scaled by a sigmoid gate: gates [n, ldg] holds the gates'
+// pre-activations (the first C columns for y0, the next C for y1), b0 and b1 their biases (float32 [C]);
+// y1 and b1 may be null (one sublayer). out float32 [n, C].
+extern "C" int qi_gated_sum(const void* gates, int gates_dtype, int ldg, const float* b0, const float* b1,
+                            const void* y0, const void* y1, int y_dtype, float* out, int n_tokens, int channels,
+                            cudaStream_t stream) {
+    QI_REQUIRE(n_tokens >= 0 && channels > 0, "gated_sum: bad sizes n=%d channels=%d", n_tokens, channels);
+    QI_REQUIRE(ldg >= (y1 ? 2 : 1) * channels, "gated_sum: the gates' rows are too short");
+    QI_REQUIRE(gates && b0 && y0 && out && (!y1 || b1), "gated_sum: an argument is missing");
+    if (n_tokens == 0) return 0;
+    const dim3 grid(blocks_for((size_t)n_tokens * channels)), block(256);
+    QI_DISPATCH_DTYPE(gates_dtype, TG, {
+        QI_DISPATCH_DTYPE(y_dtype, TY, {
+            qi::launch(gated_sum_kernel<TG, TY>, grid, block, 0, stream, (const TG*)gates, ldg, b0, b1, (const TY*)y0, (const TY*)y1,
+                       out, n_tokens, channels);
+        });
+    });
+    return qi::check_launch("gated_sum");
+}
+
+// x = cap * tanh(x / cap) in place, float32 [n].
+extern "C" int qi_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0 && cap > 0.f, "softcap: bad size or cap");
+    if (n == 0) return 0;
+    qi::launch(softcap_kernel, dim3(blocks_for((size_t)n)), dim3(256), 0, stream, x, (size_t)n, cap, 1.0f / cap);
+    return qi::check_launch("softcap");
+}

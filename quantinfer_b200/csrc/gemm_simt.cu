@@ -17,10 +17,14 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, int M,
-                 int N, int K, long long ldx, long long ldw, long long ldy) {
+                 int N, int K, long long ldx, long long ldw, long long ldy, long long sx, long long sw,
+                 long long sy) {
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     qi::pdl_enter();
+    x += (size_t)blockIdx.z * sx;      // a batch of products: one operand set per grid.z
+    w += (size_t)blockIdx.z * sw;
+    y += (size_t)blockIdx.z * sy;
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;  // tx over N, ty over M
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -75,10 +79,11 @@ gemm_simt_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restr
 
 template <typename TX, typename TW, typename TY>
 int launch(const void* x, const void* w, void* y, int M, int N, int K, long long ldx,
-           long long ldw, long long ldy, cudaStream_t stream) {
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+           long long ldw, long long ldy, cudaStream_t stream, int batch = 1, long long sx = 0, long long sw = 0,
+           long long sy = 0) {
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
     qi::launch(gemm_simt_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (const TX*)x, (const TW*)w, (TY*)y, M, N, K, ldx, ldw,
-               ldy);
+               ldy, sx, sw, sy);
     return qi::check_launch("gemm_simt");
 }
 
@@ -95,6 +100,27 @@ extern "C" int qi_gemm_simt(const void* x, int x_dtype, const void* w, int w_dty
         QI_DISPATCH_DTYPE(w_dtype, TW, {
             QI_DISPATCH_DTYPE(y_dtype, TY, {
                 return launch<TX, TW, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream);
+            });
+        });
+    });
+    return 0;
+}
+
+// A batch of such products in one launch: product b reads x + b * sx, w + b * sw and writes y + b * sy
+// (strides in elements). Per-head projections are this: the heads of one activation row lie side by
+// side (sx = the head's width, ldx = the row's), each with a weight matrix of its own.
+extern "C" int qi_gemm_simt_batched(const void* x, int x_dtype, const void* w, int w_dtype, void* y,
+                                    int y_dtype, int M, int N, int K, long long ldx, long long ldw,
+                                    long long ldy, int batch, long long sx, long long sw, long long sy,
+                                    cudaStream_t stream) {
+    QI_REQUIRE(M >= 0 && N > 0 && K > 0 && batch > 0 && batch <= 65535, "gemm_simt_batched: bad sizes M=%d N=%d K=%d batch=%d", M, N, K, batch);
+    QI_REQUIRE(ldx >= K && ldw >= K && ldy >= N, "gemm_simt_batched: a leading dimension is smaller than its row");
+    QI_REQUIRE((M + BM - 1) / BM <= 65535, "gemm_simt_batched: M=%d is too large for one launch", M);
+    if (M == 0) return 0;
+    QI_DISPATCH_DTYPE(x_dtype, TX, {
+        QI_DISPATCH_DTYPE(w_dtype, TW, {
+            QI_DISPATCH_DTYPE(y_dtype, TY, {
+                return launch<TX, TW, TY>(x, w, y, M, N, K, ldx, ldw, ldy, stream, batch, sx, sw, sy);
             });
         });
     });

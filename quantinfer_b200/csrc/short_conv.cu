@@ -1,0 +1,118 @@
+// A bank of short causal convolutions over time, one filter of `taps` weights per channel, with the
+// sequence's last taps - 1 inputs kept as state of fixed size between steps:
+//
+//     out_k[t, c] = (residual ? h[t, c] : 0) + sum_j w_k[j, c] * h[t - taps + 1 + j, c],     j = 0 .. taps - 1
+//
+// where h[s] for s before the step's first token comes from the request's state (the inputs of its
+// earlier steps) and is zero before the sequence's start. Up to two filters read the same input in one
+// launch (a layer whose sublayers each have their own filter over one normalised stream), and the
+// input can be written once more in the output type (for a consumer that reads it unfiltered).
+//
+// Inputs and state are 32-bit; sums are 32-bit; outputs in the activation type. Weights are laid out
+// [filter][tap][channel] so that a warp's loads are contiguous.
+//
+// One thread per (token, channel). A token that stands at least taps - 1 places into its entry reads
+// only the step's own rows. The thread of an entry's FIRST token also computes the entry's next
+// taps - 2 tokens (the only ones that read the old state) and then writes the new state; the threads
+// of those tokens do nothing. So the old state is read and the new one written by the same thread, in
+// program order, and one launch serves a step of any mix of portions and single tokens.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxTaps = 16;
+
+template <typename TO>
+__global__ void __launch_bounds__(256)
+short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, float* __restrict__ state,
+                  TO* __restrict__ out0, TO* __restrict__ out1, TO* __restrict__ copy,
+                  const int* __restrict__ token_req, const int* __restrict__ q_start,
+                  const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
+                  int taps, int n_filters, int residual) {
+    qi::pdl_enter();
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_tokens * C) return;
+    const int t = (int)(idx / C), c = (int)(idx % C);
+    const int e = token_req[t];
+    const int first = q_start[e];
+    const int i = t - first;
+    const float x = h[idx];
+    if (copy) copy[idx] = qi::from_f32<TO>(x);
+    const int back = taps - 1;
+    const float* w1 = w + (size_t)taps * C;
+    if (i >= back) {
+        float a0 = residual ? x : 0.f, a1 = a0;
+        for (int j = 0; j < taps; ++j) {
+            const float v = h[(size_t)(t - back + j) * C + c];
+            a0 = fmaf(w[(size_t)j * C + c], v, a0);
+            if (n_filters > 1) a1 = fmaf(w1[(size_t)j * C + c], v, a1);
+        }
+        out0[idx] = qi::from_f32<TO>(a0);
+        if (n_filters > 1) out1[idx] = qi::from_f32<TO>(a1);
+        return;
+    }
+    if (i != 0) return;
+    // the entry's first token: old state in registers, the first rows, then the new state
+    const int len = q_start[e + 1] - first;
+    const int p0 = start_pos[e];
+    float* st = state + (size_t)slot_ids[e] * back * C + c;
+    float old[kMaxTaps];
+#pragma unroll
+    for (int k = 0; k < kMaxTaps; ++k) old[k] = 0.f;
+    for (int k = 0; k < back; ++k) old[k] = (p0 - back + k >= 0) ? st[(size_t)k * C] : 0.f;
+    const int head = len < back ? len : back;
+    for (int ii = 0; ii < head; ++ii) {
+        const float xi = h[(size_t)(first + ii) * C + c];
+        float a0 = residual ? xi : 0.f, a1 = a0;
+        for (int j = 0; j < taps; ++j) {
+            const int rel = ii - back + j;      // place in the entry; negative: in the old state
+            float v;
+            if (rel >= 0) {
+                v = h[(size_t)(first + rel) * C + c];
+            } else {
+                v = 0.f;
+#pragma unroll
+                for (int k = 0; k < kMaxTaps; ++k) if (k == back + rel) v = old[k];
+            }
+            a0 = fmaf(w[(size_t)j * C + c], v, a0);
+            if (n_filters > 1) a1 = fmaf(w1[(size_t)j * C + c], v, a1);
+        }
+        out0[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(a0);
+        if (n_filters > 1) out1[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(a1);
+    }
+    for (int k = 0; k < back; ++k) {
+        const int rel = len - back + k;
+        float v;
+        if (rel >= 0) {
+            v = h[(size_t)(first + rel) * C + c];
+        } else {
+            v = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < kMaxTaps; ++kk) if (kk == back + rel) v = old[kk];
+        }
+        st[(size_t)k * C] = v;
+    }
+}
+
+}  // namespace
+
+// h float32 [n_tokens, C]; w float32 [n_filters, taps, C]; state float32 [slots, taps - 1, C] (may be null when
+// taps == 1); out0, out1 (out1 only with two filters) and copy (may be null) [n_tokens, C] in `out_dtype`.
+extern "C" int qi_short_conv(const float* h, const float* w, float* state, void* out0, void* out1, void* copy,
+                             int out_dtype, const int* token_req, const int* q_start, const int* start_pos,
+                             const int* slot_ids, int n_tokens, int channels, int taps, int n_filters, int residual,
+                             cudaStream_t stream) {
+    QI_REQUIRE(n_tokens >= 0 && channels > 0, "short_conv: bad sizes n=%d channels=%d", n_tokens, channels);
+    QI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "short_conv: %d taps are outside 1..%d", taps, kMaxTaps);
+    QI_REQUIRE(n_filters == 1 || n_filters == 2, "short_conv: one or two filters a launch, got %d", n_filters);
+    QI_REQUIRE(taps == 1 || state, "short_conv: a filter of more than one tap needs its state");
+    QI_REQUIRE(out0 && (n_filters == 1 || out1), "short_conv: an output is missing");
+    if (n_tokens == 0) return 0;
+    const size_t total = (size_t)n_tokens * channels;
+    QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "short_conv: grid too large");
+    QI_DISPATCH_DTYPE(out_dtype, TO, {
+        qi::launch(short_conv_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, h, w, state, (TO*)out0, (TO*)out1,
+                   (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps, n_filters, residual);
+    });
+    return qi::check_launch("short_conv");
+}

@@ -34,6 +34,8 @@ _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bf
            torch.float32: torch.float32, torch.bfloat16: torch.bfloat16}
 
 DEFAULT_PAGE_SIZE = 64
+DEFAULT_POOL_TOKENS = 16384   # cached tokens of a pool that nothing else sizes
+UNLIMITED = 1 << 30   # a spec's max_positions from here on means the design sets no limit
 KV_BUCKET = 512   # a decode graph serves contexts up to the next multiple of this
 
 
@@ -69,14 +71,26 @@ class Engine:
         self.page_size = page_size
         if num_pages is None:
             if max_tokens is None:
-                max_tokens = self.max_seq_len * min(max_requests, 4)
+                if max_seq_len is None and spec.max_positions >= UNLIMITED:
+                    max_tokens = DEFAULT_POOL_TOKENS     # the design sets no limit on positions to size the pool by
+                else:
+                    max_tokens = self.max_seq_len * min(max_requests, 4)
             unit = max(64, page_size)
             num_pages = -(-max_tokens // page_size)
             if unit % page_size:
                 num_pages += max_requests  # pages that do not divide the rounding unit need slack
+        if max_seq_len is None and spec.max_positions >= UNLIMITED:
+            # a design without a limit of its own: a request is as long as the pool lets it be (block tables
+            # are sized by this)
+            self.max_seq_len = num_pages * page_size
         self.cache = CacheManager(self.model.cache_needs, page_size, num_pages, max_requests,
                                   self.max_seq_len, self.dtype, self.device)
         self._views = [self.cache.view(call.cache, call.writes_cache) for call in self.model.order]
+        for view, entry in zip(self._views, self.model.call_state_entry):
+            if entry is not None:
+                view.state = self.cache.states[entry]      # the call's own state of fixed size, beside its pages
+        if self.model.embedding_state_entry is not None:
+            self.model.embedding_view = self.cache.view(self.model.embedding_state_entry)
         from ..sampling.slots import RequestSlots
 
         self.slots = RequestSlots(max_requests, self.device)   # the sampler's record of every slot, on the device

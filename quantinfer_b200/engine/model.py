@@ -43,15 +43,33 @@ class Model:
         self.order = spec.order
         self.native = None            # the C++ driver's description of this model (engine/native.py), once asked for
         self.use_native = True
-        # what each cache entry must hold comes from the layer that writes it
+        # what each cache entry must hold comes from the layer that writes it, widened by those that read it
+        # (a reader with a longer window than the writer's keeps the entry's pages that much longer)
         self.cache_needs = [None] * spec.cache_entries()
         for call in self.order:
             if call.writes_cache:
                 self.cache_needs[call.cache] = self.blocks[call.layer].cache_need()
         for call in self.order:
-            if not call.writes_cache and self.blocks[call.layer].cache_need() != self.cache_needs[call.cache]:
-                raise ConfigError(
-                    f"layer {call.layer} reads cache entry {call.cache}, whose writer keeps something else")
+            if not call.writes_cache:
+                have, want = self.cache_needs[call.cache], self.blocks[call.layer].cache_need()
+                merged = have if have == want else (have.merged(want) if hasattr(have, "merged") else None)
+                if merged is None:
+                    raise ConfigError(
+                        f"layer {call.layer} reads cache entry {call.cache}, whose writer keeps something else")
+                self.cache_needs[call.cache] = merged
+        # state of fixed size that parts keep besides the mixers' entries: one more entry per layer call whose
+        # block asks for it (`state_need`), and one for the embedding; the engine hands each its view
+        self.call_state_entry = []
+        for call in self.order:
+            need = getattr(self.blocks[call.layer], "state_need", lambda: None)()
+            self.call_state_entry.append(len(self.cache_needs) if need is not None else None)
+            if need is not None:
+                self.cache_needs.append(need)
+        need = getattr(self.embedding, "state_need", lambda: None)()
+        self.embedding_state_entry = len(self.cache_needs) if need is not None else None
+        if need is not None:
+            self.cache_needs.append(need)
+        self.embedding_view = None     # set by the engine when the embedding keeps state
 
     def _parts(self):
         return (self.embedding, *self.blocks, self.final_norm, self.head)
@@ -87,7 +105,10 @@ class Model:
                 self.native = NativeProgram.build(self, cache_views) or False
             if self.native:
                 return self.native.forward(batch)
-        resid = self.embedding(batch.token_ids)
+        if self.embedding_state_entry is not None:
+            resid = self.embedding(batch.token_ids, batch, self.embedding_view)
+        else:
+            resid = self.embedding(batch.token_ids)
         delta = None
         for call, view in zip(self.order, cache_views):
             resid, delta = self.blocks[call.layer].forward(resid, delta, batch, view)

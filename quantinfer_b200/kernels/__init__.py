@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 
 def status_names(code: int) -> list:
@@ -740,3 +740,172 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, out, plan=None, status=None, epi
                                 BF16 if partial_only else _code(out), M, N, K, int(swap), bn, splits, epi,
                                 _ptr(ws), _ptr(status), _stream())
     return ws if partial_only else out
+
+
+# --------------------------------------------------------------------------
+# bigram embedding, short convolutions, per-head products, gates, soft cap
+
+
+def embedding_bigram(table, bigram, ids, positions, token_req, q_start, slot_ids, prev_state, out, buckets: int,
+                     mul_prev: int, mul_cur: int, status) -> None:
+    """out[t] = table[ids[t]] + bigram[row_t] as float32: row_t = (previous id * mul_prev + ids[t] * mul_cur) mod
+    buckets, or the row `buckets` for a sequence's first token. `prev_state` (int32, one word a slot) carries a
+    request's last token from step to step; the launch reads and advances it."""
+    _req(table, "table", ndim=2)
+    _req(bigram, "bigram", table.dtype, 2)
+    _req(out, "out", torch.float32, 2)
+    for t, name in ((ids, "ids"), (positions, "positions"), (token_req, "token_req"), (q_start, "q_start"),
+                    (slot_ids, "slot_ids"), (prev_state, "prev_state")):
+        _req(t, name, torch.int32)
+    n, hidden = out.shape
+    if ids.numel() != n or table.shape[1] != hidden or tuple(bigram.shape) != (buckets + 1, hidden):
+        raise KernelError(f"embedding_bigram: shapes do not agree: table {tuple(table.shape)}, bigram {tuple(bigram.shape)} "
+                          f"for {buckets} buckets, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    _call("other", "embedding_bigram", library().qi_embedding_bigram,
+          _ptr(table), _ptr(bigram), _code(table), _ptr(ids), _ptr(positions), _ptr(token_req), _ptr(q_start),
+          _ptr(slot_ids), _ptr(prev_state), _ptr(out), n, hidden, table.shape[0], C.c_longlong(buckets),
+          C.c_longlong(mul_prev), C.c_longlong(mul_cur), _ptr(status), _stream())
+
+
+def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slot_ids, residual: bool = True) -> None:
+    """outs[k][t] = (h[t] if residual) + sum_j weights[k, j] * h[t - taps + 1 + j] per channel, over each request's
+    own time axis: rows before a step's first token come from `state` (float32 [slots, taps - 1, channels], the
+    request's last inputs; advanced by the launch), zeros before the sequence's start. h float32 [n, channels];
+    weights float32 [filters, taps, channels] with one or two filters; `copy`, if given, receives h in its type."""
+    _req(h, "h", torch.float32, 2)
+    _req(weights, "weights", torch.float32, 3)
+    n, ch = h.shape
+    filters, taps = weights.shape[0], weights.shape[1]
+    if weights.shape[2] != ch or len(outs) != filters:
+        raise KernelError(f"short_conv: weights {tuple(weights.shape)} and {len(outs)} outputs do not fit h {tuple(h.shape)}")
+    for o in list(outs) + ([copy] if copy is not None else []):
+        _req(o, "out", outs[0].dtype, 2)
+        if tuple(o.shape) != (n, ch):
+            raise KernelError(f"short_conv: an output is {tuple(o.shape)}, expected {(n, ch)}")
+    if taps > 1:
+        _req(state, "state", torch.float32, 3)
+        if tuple(state.shape[1:]) != (taps - 1, ch):
+            raise KernelError(f"short_conv: state {tuple(state.shape)} does not fit {taps} taps of {ch} channels")
+    for t, name in ((token_req, "token_req"), (q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32)
+    _call("other", "short_conv", library().qi_short_conv,
+          _ptr(h), _ptr(weights), _ptr(state if taps > 1 else None), _ptr(outs[0]), _ptr(outs[1] if filters > 1 else None),
+          _ptr(copy), _code(outs[0]), _ptr(token_req), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), n, ch, taps, filters,
+          int(bool(residual)), _stream())
+
+
+def head_linear(x, x_head_width: int, x_offset: int, k: int, w, out, out_head_width: int, out_offset: int) -> None:
+    """Per-head projections in one launch. Heads lie side by side in the rows of x [n, >= heads * x_head_width] and
+    of out [n, >= heads * out_head_width]; for head h,
+        out[:, h * out_head_width + out_offset : ... + N] = x[:, h * x_head_width + x_offset : ... + k] @ w[h]^T
+    with w [heads, N, k]. 32-bit products and sums; any element types."""
+    _req(x, "x", ndim=2)
+    _req(w, "w", ndim=3)
+    _req(out, "out", ndim=2)
+    n = x.shape[0]
+    heads, N = w.shape[0], w.shape[1]
+    if (w.shape[2] != k or out.shape[0] != n or x_offset + k > x_head_width or out_offset + N > out_head_width
+            or heads * x_head_width > x.shape[1] or heads * out_head_width > out.shape[1]):
+        raise KernelError(f"head_linear: x {tuple(x.shape)} (heads of {x_head_width}), w {tuple(w.shape)}, out {tuple(out.shape)} "
+                          f"(heads of {out_head_width}) do not fit")
+    _call("gemm", "head_linear", library().qi_gemm_simt_batched,
+          C.c_void_p(x.data_ptr() + x_offset * x.element_size()), _code(x), _ptr(w), _code(w),
+          C.c_void_p(out.data_ptr() + out_offset * out.element_size()), _code(out), n, N, k, C.c_longlong(x.shape[1]),
+          C.c_longlong(k), C.c_longlong(out.shape[1]), heads, C.c_longlong(x_head_width), C.c_longlong(N * k),
+          C.c_longlong(out_head_width), _stream())
+
+
+def activation(x, out, name: str) -> None:
+    """out = act(x), elementwise, x and out of one type and shape."""
+    if name not in ACTIVATIONS:
+        raise KernelError(f"activation: {name!r} has no kernel (one of {sorted(ACTIVATIONS)})")
+    _req(x, "x")
+    _req(out, "out", x.dtype)
+    if out.shape != x.shape:
+        raise KernelError("activation: shapes differ")
+    _call("other", "activation", library().qi_activation, _ptr(x), _ptr(out), _code(x), C.c_longlong(x.numel()),
+          ACTIVATIONS[name], _stream())
+
+
+def gated_sum(gates, b0, b1, y0, y1, out) -> None:
+    """out = sigmoid(gates[:, :C] + b0) * y0 (+ sigmoid(gates[:, C:2C] + b1) * y1 when y1 is given); out float32
+    [n, C], biases float32 [C], y0 and y1 of one type."""
+    _req(gates, "gates", ndim=2)
+    _req(out, "out", torch.float32, 2)
+    _req(y0, "y0", ndim=2)
+    _req(b0, "b0", torch.float32, 1)
+    n, ch = out.shape
+    if y1 is not None:
+        _req(y1, "y1", y0.dtype, 2)
+        _req(b1, "b1", torch.float32, 1)
+    if (gates.shape[0] != n or gates.shape[1] < (2 if y1 is not None else 1) * ch or tuple(y0.shape) != (n, ch)
+            or b0.numel() != ch or (y1 is not None and (tuple(y1.shape) != (n, ch) or b1.numel() != ch))):
+        raise KernelError(f"gated_sum: gates {tuple(gates.shape)}, y {tuple(y0.shape)}, out {tuple(out.shape)} do not fit")
+    _call("other", "gated_sum", library().qi_gated_sum, _ptr(gates), _code(gates), gates.shape[1], _ptr(b0), _ptr(b1),
+          _ptr(y0), _ptr(y1), _code(y0), _ptr(out), n, ch, _stream())
+
+
+def softcap(x, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place; x float32."""
+    _req(x, "x", torch.float32)
+    _call("other", "softcap", library().qi_softcap, _ptr(x), C.c_longlong(x.numel()), C.c_float(cap), _stream())
+
+
+# --------------------------------------------------------------------------
+# attention over a cached latent
+
+
+def latent_prepare(proj, kv_offset, q_out, gain, eps: float, inv_freq, rot_dims: int, positions, token_req,
+                   block_table, cache, heads: int, d: int, r: int, rank: int, status) -> None:
+    """From the fused projection's rows [heads x (d + r) | latent projection (rank + r) at column kv_offset]: rotates
+    every head's r-part into q_out[:, h, rank:], and, unless kv_offset is None, normalises the latent (gain float32
+    [rank]), rotates the shared key part and writes [latent | key part] into `cache` [pages, page_size, rank + r] at
+    each token's position. Pairs (2i, 2i + 1) of the part's first rot_dims coordinates turn by position * inv_freq[i]."""
+    _req(proj, "proj", ndim=2)
+    _req(q_out, "q_out", ndim=3)
+    n = proj.shape[0]
+    if tuple(q_out.shape) != (n, heads, rank + r):
+        raise KernelError(f"latent_prepare: q_out {tuple(q_out.shape)} is not {(n, heads, rank + r)}")
+    if rot_dims:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() * 2 != rot_dims:
+            raise KernelError("latent_prepare: inv_freq does not match rot_dims")
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    page_size = num_pages = max_blocks = 0
+    if kv_offset is not None:
+        _req(cache, "cache", q_out.dtype, 3)
+        _req(gain, "gain", torch.float32, 1)
+        _req(block_table, "block_table", torch.int32, 2)
+        if cache.shape[2] != rank + r or gain.numel() != rank:
+            raise KernelError(f"latent_prepare: cache {tuple(cache.shape)} / gain {gain.numel()} do not fit rank {rank} + {r}")
+        num_pages, page_size, max_blocks = cache.shape[0], cache.shape[1], block_table.shape[1]
+    _call("rope", "latent_prepare", library().qi_latent_prepare,
+          _ptr(proj), _code(proj), C.c_longlong(proj.shape[1]), -1 if kv_offset is None else int(kv_offset), _ptr(q_out),
+          _code(q_out), _ptr(gain if kv_offset is not None else None), C.c_float(eps), _ptr(inv_freq if rot_dims else None),
+          rot_dims, _ptr(positions), _ptr(token_req), _ptr(block_table if kv_offset is not None else None), max_blocks,
+          page_size, num_pages, _ptr(cache if kv_offset is not None else None), n, heads, d, r, rank, _ptr(status), _stream())
+
+
+def latent_attention_generic(q, out, cache, sink, block_table, positions, token_req, scale: float, window: int, status) -> None:
+    """Causal attention of every head over one shared cached row per position: q [n, heads, W], cache [pages,
+    page_size, W], out [n, heads, R] = sum_j p_j cache[j, :R]; the softmax's denominator also holds exp(sink[h])
+    when `sink` (float32 [heads]) is given. 32-bit arithmetic, any sizes."""
+    _req(q, "q", ndim=3)
+    _req(out, "out", q.dtype, 3)
+    _req(cache, "cache", q.dtype, 3)
+    _req(block_table, "block_table", torch.int32, 2)
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    n, heads, W = q.shape
+    R = out.shape[2]
+    if out.shape[0] != n or out.shape[1] != heads or cache.shape[2] != W or R > W:
+        raise KernelError(f"latent_attention: q {tuple(q.shape)}, out {tuple(out.shape)}, cache {tuple(cache.shape)} do not fit")
+    if sink is not None:
+        _req(sink, "sink", torch.float32, 1)
+        if sink.numel() != heads:
+            raise KernelError("latent_attention: one sink a head")
+    _call("attention", "latent_attention_generic", library().qi_latent_attention_generic,
+          _ptr(q), _ptr(out), _code(q), _ptr(cache), _ptr(sink), _ptr(block_table), block_table.shape[1], cache.shape[1],
+          cache.shape[0], _ptr(positions), _ptr(token_req), n, heads, W, R, C.c_float(scale), int(window or 0), _ptr(status),
+          _stream())

@@ -50,7 +50,7 @@ import torch
 
 from ..errors import ConfigError
 
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "conv")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

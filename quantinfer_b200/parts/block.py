@@ -10,7 +10,13 @@ attention :128-129, add :130, norm :131-135, feed-forward and add :136-137).
 
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
+from ..errors import ConfigError
+from ..weights.loader import TensorNeed
 from .base import Part, build_part, part_class, register_part
+from .linear import Linear
 
 
 class PreNormBlock(Part):
@@ -44,4 +50,90 @@ class PreNormBlock(Part):
         return resid, self.ffn.forward(x)
 
 
+class ParallelGatedBlock(Part):
+    """One norm, two sublayers side by side, gated:
+
+        h = norm(x) ; x = x + gate_m * mixer(conv_m(h)) + gate_f * ffn(conv_f(h))
+        gate_k = sigmoid(h . Wg_k^T + b_k)          conv_k(h) = h + filter_k(h) over time
+
+    The norm's output stays 32-bit: it is the input of the convolutions (whose state is 32-bit) and is
+    written once more in the activation type for the gates' projection, which reads it unfiltered. The gates'
+    matrices are stacked at load, so one product gives both; the two biases, the sigmoids, the products with
+    the sublayers' outputs and their sum are one kernel whose 32-bit result the next norm adds to the stream.
+    The input convolutions are optional (absent from the spec: h goes to the sublayers as it is); so is the
+    feed-forward. The gates are what makes this block: a spec without them is refused."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.norm = build_part("norm", spec.norm, runtime)
+        self.mixer = build_part("mixer", spec.mixer, runtime)
+        self.ffn = build_part("ffn", spec.ffn, runtime) if spec.ffn is not None else None
+        self.conv = build_part("conv", spec.conv, runtime) if spec.conv is not None else None
+        n_sub = 2 if self.ffn is not None else 1
+        if self.conv is not None and len(spec.conv.names) != n_sub:
+            raise ConfigError("parallel_gated: one input filter per sublayer")
+        if spec.gate_names is not None and len(spec.gate_names) != n_sub:
+            raise ConfigError("parallel_gated: one gate per sublayer")
+        if spec.gate_names is None:
+            raise ConfigError("parallel_gated: the spec names no gates")
+        h = spec.norm.size
+        self.gates = Linear(runtime, n_sub * h, h, spec.gate_names[0] + "+")
+        self.gate_bias = None
+        self._parts = tuple(p for p in (self.norm, self.mixer, self.ffn, self.conv) if p is not None)
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        needs = {}
+        subs = [("norm", spec.norm), ("mixer", spec.mixer)]
+        if spec.ffn is not None:
+            subs.append(("ffn", spec.ffn))
+        if spec.conv is not None:
+            subs.append(("conv", spec.conv))
+        for cat, sub in subs:
+            needs.update(part_class(cat, sub).needs_of_spec(sub))
+        h = spec.norm.size
+        for name in spec.gate_names or ():
+            needs[name] = TensorNeed((h, h))
+            needs[name + ".b"] = TensorNeed((h,), "matrix", "zeros")
+        return needs
+
+    def load(self, tensors):
+        for p in self._parts:
+            p.load(tensors)
+        names = self.spec.gate_names
+        if names is not None:
+            ws = [tensors[n] for n in names]
+            if len({w.dtype for w in ws}) > 1:
+                ws = [w.to(torch.float32) for w in ws]
+            self.gates.load(torch.cat(ws, dim=0))
+            self.gate_bias = [self._gain(tensors[n + ".b"]) for n in names]
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def state_need(self):
+        return self.conv.state_need() if self.conv is not None else None
+
+    def forward(self, resid, delta, batch, cache):
+        rt = self.runtime
+        n, width = resid.shape
+        two = self.ffn is not None
+        if self.conv is not None:
+            h = torch.empty((n, width), dtype=torch.float32, device=resid.device)
+            kernels.add_rmsnorm(resid, delta, self.norm.gain, self.norm.spec.eps, h)
+            ins, hb = self.conv.forward(h, batch, cache.state, want_copy=rt.dtype != torch.float32)
+            if hb is None:
+                hb = h
+        else:
+            hb = self.norm(resid, delta)
+            ins = [hb, hb]
+        y_m = self.mixer.forward(ins[0], batch, cache)
+        y_f = self.ffn.forward(ins[1]) if two else None
+        out = torch.empty((n, width), dtype=torch.float32, device=resid.device)
+        g = self.gates(hb)
+        kernels.gated_sum(g, self.gate_bias[0], self.gate_bias[1] if two else None, y_m, y_f, out)
+        return resid, out
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel_gated", ParallelGatedBlock)

@@ -51,4 +51,33 @@ class GatedMLP(Part):
     __call__ = forward
 
 
+class DenseMLP(Part):
+    """Feed-forward without a gate: y = down(act(up(x))), no biases; tensors `prefix + "up"` [I, H] and
+    `prefix + "down"` [H, I]. The activation runs in 32-bit over the product's output."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        if spec.activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"dense_mlp: activation {spec.activation!r} has no kernel (one of {sorted(kernels.ACTIVATIONS)})")
+        self.up = Linear(runtime, spec.intermediate_size, spec.hidden_size, spec.prefix + "up")
+        self.down = Linear(runtime, spec.hidden_size, spec.intermediate_size, spec.prefix + "down")
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        h, i, p = spec.hidden_size, spec.intermediate_size, spec.prefix
+        return {p + "up": TensorNeed((i, h)), p + "down": TensorNeed((h, i))}
+
+    def load(self, tensors):
+        self.up.load(tensors[self.spec.prefix + "up"])
+        self.down.load(tensors[self.spec.prefix + "down"])
+
+    def forward(self, x):
+        u = self.up(x)
+        kernels.activation(u, u, self.spec.activation)
+        return self.down(u)
+
+    __call__ = forward
+
+
 register_part("ffn", "gated_mlp", GatedMLP)
+register_part("ffn", "dense_mlp", DenseMLP)

@@ -49,4 +49,19 @@ class RMSNorm(Part):
     __call__ = forward
 
 
+class ScalarRMSNorm(RMSNorm):
+    """RMS norm whose gain is ONE number for all coordinates, stored as a tensor of shape [] under the
+    spec's `prefix` itself. The number is spread over a gain vector at load, so the fused kernels of the
+    per-coordinate norm serve it unchanged."""
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        return {spec.prefix: TensorNeed((), "gain", "gain")}
+
+    def load(self, tensors):
+        g = tensors[self.spec.prefix].to(torch.float32).reshape(1)
+        self.gain = self._gain(g.expand(self.spec.size))
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)
