@@ -808,11 +808,18 @@ def head_linear(x, x_head_width: int, x_offset: int, k: int, w, out, out_head_wi
             or heads * x_head_width > x.shape[1] or heads * out_head_width > out.shape[1]):
         raise KernelError(f"head_linear: x {tuple(x.shape)} (heads of {x_head_width}), w {tuple(w.shape)}, out {tuple(out.shape)} "
                           f"(heads of {out_head_width}) do not fit")
-    _call("gemm", "head_linear", library().qi_gemm_simt_batched,
-          C.c_void_p(x.data_ptr() + x_offset * x.element_size()), _code(x), _ptr(w), _code(w),
-          C.c_void_p(out.data_ptr() + out_offset * out.element_size()), _code(out), n, N, k, C.c_longlong(x.shape[1]),
-          C.c_longlong(k), C.c_longlong(out.shape[1]), heads, C.c_longlong(x_head_width), C.c_longlong(N * k),
-          C.c_longlong(out_head_width), _stream())
+    xp = x.data_ptr() + x_offset * x.element_size()
+    op = out.data_ptr() + out_offset * out.element_size()
+    strides = (C.c_longlong(x.shape[1]), C.c_longlong(k), C.c_longlong(out.shape[1]))
+    batch = (heads, C.c_longlong(x_head_width), C.c_longlong(N * k), C.c_longlong(out_head_width))
+    lib = library()
+    if (x.dtype == w.dtype == out.dtype == torch.bfloat16 and lib.qi_gemm_mma_batched_supported(
+            C.c_void_p(xp), _ptr(w), C.c_void_p(op), k, *strides, *batch[1:])):
+        # bfloat16 throughout and aligned for 16-byte loads: the tensor-core kernel
+        _call("gemm", "head_linear", lib.qi_gemm_mma_batched, C.c_void_p(xp), _ptr(w), C.c_void_p(op), n, N, k, *strides, *batch, _stream())
+        return
+    _call("gemm", "head_linear", lib.qi_gemm_simt_batched, C.c_void_p(xp), _code(x), _ptr(w), _code(w), C.c_void_p(op), _code(out),
+          n, N, k, *strides, *batch, _stream())
 
 
 def activation(x, out, name: str) -> None:
@@ -908,4 +915,39 @@ def latent_attention_generic(q, out, cache, sink, block_table, positions, token_
     _call("attention", "latent_attention_generic", library().qi_latent_attention_generic,
           _ptr(q), _ptr(out), _code(q), _ptr(cache), _ptr(sink), _ptr(block_table), block_table.shape[1], cache.shape[1],
           cache.shape[0], _ptr(positions), _ptr(token_req), n, heads, W, R, C.c_float(scale), int(window or 0), _ptr(status),
+          _stream())
+
+
+def latent_attention_mma_supported(W: int, R: int) -> bool:
+    """Whether the tensor-core latent attention takes rows of W with a latent of R (bfloat16 only)."""
+    return bool(library().qi_latent_attention_mma_supported(W, R))
+
+
+def latent_attention(q, out, cache, sink, block_table, q_start, start_pos, positions, token_req, scale: float, window: int,
+                     status, impl: str | None = None) -> None:
+    """`latent_attention_generic`'s result by the kernel that fits: "mma" (bfloat16, latent widths the tensor-core
+    kernel covers: flash form, one key tile for all heads) or "generic". `q_start`, `start_pos`: the step's per-entry
+    arrays (the tensor-core kernel finds its query tiles from them on the device)."""
+    n, heads, W = q.shape
+    R = out.shape[2]
+    if impl is None:
+        impl = "mma" if q.dtype == torch.bfloat16 and latent_attention_mma_supported(W, R) else "generic"
+    if impl == "generic":
+        return latent_attention_generic(q, out, cache, sink, block_table, positions, token_req, scale, window, status)
+    if impl != "mma":
+        raise KernelError(f"latent_attention: unknown kernel {impl!r}")
+    _req(q, "q", torch.bfloat16, 3)
+    _req(out, "out", torch.bfloat16, 3)
+    _req(cache, "cache", torch.bfloat16, 3)
+    for t, name in ((block_table, "block_table"), (q_start, "q_start"), (start_pos, "start_pos")):
+        _req(t, name, torch.int32)
+    if out.shape[0] != n or out.shape[1] != heads or cache.shape[2] != W or q_start.numel() != start_pos.numel() + 1:
+        raise KernelError(f"latent_attention: q {tuple(q.shape)}, out {tuple(out.shape)}, cache {tuple(cache.shape)} do not fit")
+    if sink is not None:
+        _req(sink, "sink", torch.float32, 1)
+        if sink.numel() != heads:
+            raise KernelError("latent_attention: one sink a head")
+    _call("attention", "latent_attention_mma", library().qi_latent_attention_mma,
+          _ptr(q), _ptr(out), _ptr(cache), _ptr(sink), _ptr(block_table), block_table.shape[1], cache.shape[1], cache.shape[0],
+          _ptr(q_start), _ptr(start_pos), start_pos.numel(), n, heads, W, R, C.c_float(scale), int(window or 0), _ptr(status),
           _stream())

@@ -25,7 +25,7 @@ DEV = "cuda:0"
 # |engine - plain float64| on logits that the soft cap keeps within a few units. float32: order of sums and the
 # device's exp, tanh, sin, cos. bfloat16: three times the worst error measured per configuration.
 TOL_F32 = 4e-5
-TOL_BF16_MEASURED = {"P": 0.057, "Q": 0.104, "R": 0.035, "S": 0.060, "T": 0.116}
+TOL_BF16_MEASURED = {"P": 0.057, "Q": 0.090, "R": 0.035, "S": 0.060, "T": 0.116}
 LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 150, 5], "R": [50, 33, 80, 17, 64],
            "S": [90, 41, 120, 8, 64, 33], "T": [60, 100, 31, 64, 9, 70]}
 
@@ -186,6 +186,88 @@ def test_scalar_norm_and_dense_feed_forward_parts(dtype):
     y = ff.forward(x.to(DEV))
     ref = plain.dense_ff(x.float(), w["f.up"].float(), w["f.down"].float())
     assert float((y.float().cpu() - ref).abs().max()) < (2e-5 if dtype == torch.float32 else 4e-2)
+
+
+@pytest.mark.parametrize("R, r, H, window, page", [(64, 16, 6, 40, 64), (32, 16, 1, None, 8), (128, 64, 8, 17, 16),
+                                                    (64, 32, 70, 33, 32), (256, 64, 3, 100, 16), (32, 32, 64, 1, 8)])
+def test_tensor_core_latent_attention_against_float64(R, r, H, window, page):
+    """The flash kernel alone on a batch of three decode tokens in front of portions of 2, 130 and 37 tokens that
+    start in the middle of pages, over shuffled pages; one far key of the long request is made to dominate; the
+    pages before every window hold NaN (they may be free again and must not be read into the sums)."""
+    from quantinfer_b200 import kernels
+
+    torch.manual_seed(R + r + H)
+    W = R + r
+    lengths, starts = [1, 1, 1, 2, 130, 37], [0, 63, 200, 14, 9, 250]
+    n_req, max_blocks = len(lengths), 48
+    num_pages = sum(-(-(s + n) // page) for s, n in zip(starts, lengths)) + 3
+    order = torch.randperm(num_pages).tolist()
+    table = torch.full((n_req, max_blocks), -1, dtype=torch.int32)
+    cache = torch.full((num_pages, page, W), float("nan"), dtype=torch.bfloat16)
+    rows = []
+    for e, (s, n) in enumerate(zip(starts, lengths)):
+        kv = (torch.randn(s + n, W) * 0.7).to(torch.bfloat16)
+        if e == 4:
+            kv[20, R:] *= 6.0            # a far key whose rotated part stands out
+        lo = 0 if window is None else max(0, s - window + 1)
+        for b in range(lo // page, -(-(s + n) // page)):
+            pg = order.pop()
+            table[e, b] = pg
+            seg = kv[b * page:(b + 1) * page]
+            cache[pg, :seg.shape[0]] = seg
+            if b * page < lo:
+                cache[pg, :lo - b * page] = float("nan")      # before the first query's window: never to be used
+        rows.append(kv)
+    n = sum(lengths)
+    q = (torch.randn(n, H, W) * 0.7).to(torch.bfloat16)
+    sink = torch.randn(H)
+    scale = 1.0 / math.sqrt(W)
+    ref = torch.zeros(n, H, R, dtype=torch.float64)
+    t = 0
+    for e, (s, ln) in enumerate(zip(starts, lengths)):
+        for i in range(ln):
+            p = s + i
+            lo = 0 if window is None else max(0, p - window + 1)
+            kv = rows[e][lo:p + 1].double()
+            sc = torch.einsum("hw,jw->hj", q[t].double(), kv) * scale
+            mx = torch.maximum(sc.max(dim=1).values, sink.double())
+            ex = torch.exp(sc - mx[:, None])
+            ref[t] = (ex / (ex.sum(dim=1) + torch.exp(sink.double() - mx))[:, None]) @ kv[:, :R]
+            t += 1
+    q_start, token_req, positions, start_pos, _ = _state_batch(lengths, starts, list(range(n_req)))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    outs = {}
+    for impl in ("mma", "generic"):
+        out = torch.full((n, H, R), 7.0, dtype=torch.bfloat16, device=DEV)
+        kernels.latent_attention(q.to(DEV), out, cache.to(DEV), sink.to(DEV), table.to(DEV), q_start, start_pos, positions,
+                                 token_req, scale, window or 0, status, impl=impl)
+        outs[impl] = out.float().cpu().double()
+        err = (outs[impl] - ref).abs().amax(dim=(1, 2))
+        assert float(err.max()) < 0.03, (impl, int(err.argmax()), float(err.max()))
+    assert int(status.item()) == 0
+    table[4, (starts[4] + 60) // page] = -1                  # a page the long portion needs is missing: flagged, not read
+    out = torch.empty((n, H, R), dtype=torch.bfloat16, device=DEV)
+    kernels.latent_attention(q.to(DEV), out, cache.to(DEV), sink.to(DEV), table.to(DEV), q_start, start_pos, positions, token_req,
+                             scale, window or 0, status, impl="mma")
+    assert int(status.item()) == kernels.STATUS_BAD_PAGE
+
+
+@pytest.mark.parametrize("n, heads, k, N", [(5, 6, 64, 64), (200, 3, 32, 80), (64, 70, 128, 16), (1, 2, 8, 8)])
+def test_tensor_core_head_products_against_float64(n, heads, k, N):
+    from quantinfer_b200 import kernels
+
+    torch.manual_seed(n)
+    xw, ow = k + 16, N + 8
+    x, w = torch.randn(n, heads * xw + 8).to(torch.bfloat16), (torch.randn(heads, N, k) / math.sqrt(k)).to(torch.bfloat16)
+    out = torch.zeros(n, heads * ow, dtype=torch.bfloat16, device=DEV)
+    before = kernels.launches
+    kernels.head_linear(x.to(DEV), xw, 8, k, w.to(DEV), out, ow, 2)
+    assert kernels.launches == before + 1
+    for h in range(heads):
+        ref = x[:, h * xw + 8:h * xw + 8 + k].double() @ w[h].double().t()
+        got = out.cpu()[:, h * ow + 2:h * ow + 2 + N].double()
+        assert float((got - ref).abs().max()) < 0.02 * max(1.0, float(ref.abs().max())), h
+        assert float(out.cpu()[:, h * ow:h * ow + 2].abs().max()) == 0.0
 
 
 # ---------------------------------------------------------------- the mixer alone, with inputs made to show faults
