@@ -132,8 +132,34 @@ class ClockSampler:
         return out
 
 
+def latent_arithmetic(config, spec):
+    """The same for a model of latent-attention layers (the Bebuvik design): projections of q and of the latent,
+    the per-head products into and out of the latent space, output projection, dense feed-forward, gates. A
+    layer's attention reads one row of kv_rank + rot_dim per visible position, whether it wrote it or not."""
+    L, H, V = len(spec.layers), spec.hidden_size, spec.vocab_size
+    params, rows, flops_per_key = 0, 0, 0
+    for layer in config.layers:
+        m = layer.mixer
+        params += H * m.heads * (m.dim + m.rot_dim) + (0 if m.kv_from is not None else H * (m.kv_rank + m.rot_dim))
+        params += m.heads * m.kv_rank * (m.dim + m.vdim) + m.heads * m.vdim * H + H * H
+        if layer.ff is not None:
+            params += 2 * H * layer.ff + H * H
+        rows += m.kv_rank + m.rot_dim
+        flops_per_key += 2.0 * m.heads * (2 * m.kv_rank + m.rot_dim)
+    m0 = config.layers[0].mixer
+    window = min((l.mixer.window or (1 << 30)) for l in config.layers)
+    a = dict(L=L, H=H, I=config.layers[0].ff, V=V, nq=m0.heads, nkv=1, d=m0.dim + m0.rot_dim, layer_params=params / L)
+    a["weight_bytes"] = 2 * (params + V * H)
+    a["kv_bytes_per_token"] = 2 * rows
+    a["gemm_flops"] = lambda T, rows_=1: 2.0 * T * params + 2.0 * H * V * rows_
+    a["attn_flops"] = lambda T: flops_per_key * sum(min(t + 1, window) for t in range(T))
+    return a
+
+
 def model_arithmetic(config, spec):
     """Parameter counts, bytes and flops of the configuration (every matrix bf16)."""
+    if hasattr(config, "layers"):
+        return latent_arithmetic(config, spec)
     L, H, I, V = len(spec.layers), spec.hidden_size, config.intermediate_size, spec.vocab_size
     nq, nkv, d = config.num_attention_heads, config.num_key_value_heads, config.effective_head_dim
     layer_params = H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I
@@ -153,7 +179,9 @@ def build_engine(args, entry, context, max_requests, pool_tokens):
     from quantinfer_b200.weights import random_tensors
 
     cfg_d = dict(entry["config"])
-    if args.layers:
+    if args.layers and "layers" in cfg_d:
+        cfg_d["layers"] = cfg_d["layers"][:args.layers]
+    elif args.layers:
         cfg_d["num_hidden_layers"] = args.layers
     config = config_from_dict(cfg_d)
     spec = config.to_model_spec()
@@ -385,6 +413,93 @@ class Bench:
         return {"prefill_kernel_us": round(us, 1), "prefill_kernel_tflops": round(tf, 1), "prefill_kernel_frac_burst": round(tf / burst, 3)}
 
 
+# ---- the latent-attention design beside the dense one at equal layer sizes ---------------------------------
+# (width, heads, plain + rotated query/key size, value size, latent, feed-forward): a dense feed-forward of two
+# matrices of ff against a gated one of three matrices of 2 ff / 3; the dense model's heads are of the query/key size
+COMPARE_SIZES = {
+    "2048": dict(width=2048, heads=16, dim=64, rot=64, vdim=128, rank=256, ff=8192),
+    "4096": dict(width=4096, heads=32, dim=64, rot=64, vdim=128, rank=256, ff=12288),
+    "5120": dict(width=5120, heads=40, dim=64, rot=64, vdim=128, rank=128, ff=17408),
+}
+COMPARE_LAYERS, COMPARE_VOCAB, COMPARE_PROMPT, COMPARE_BATCH = 4, 32768, 2048, 8
+
+
+def compare_entries(size):
+    z = COMPARE_SIZES[size]
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+             "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 1000000.0, "dims": z["rot"]}, "mask": {"size": 4096}}
+    shares = {1: 0, 3: 2}        # every second layer reads the latent of the layer before it
+    layers = [{"type": "latent_attention", "mixer": dict(mixer, **({"kv_from": shares[i]} if i in shares else {})),
+               "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(COMPARE_LAYERS)]
+    latent = dict(architecture="Bebuvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, canon={"taps": 4},
+                  embedding={"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 7}}, logit_softcap=30.0, layers=layers)
+    dense = dict(_COMMON, vocab_size=COMPARE_VOCAB, hidden_size=z["width"], intermediate_size=(2 * z["ff"] // 3 + 127) // 128 * 128,
+                 num_hidden_layers=COMPARE_LAYERS, num_attention_heads=z["heads"], head_dim=z["dim"] + z["rot"])
+    common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())
+    return (dict(common, config=latent, name=f"Bebuvik layers of width {size}"),
+            dict(common, config=dense, name=f"Qwen3 layers of width {size}"))
+
+
+def compare_designs(args):
+    """Prefill and decode throughput of latent-attention layers and of dense GQA layers of the same width, head
+    count, query/key size, depth and vocabulary, and every kernel class of each alone with its share of the roofline."""
+    import gc
+
+    import torch
+
+    from quantinfer_b200 import kernels
+
+    hbm, sustained, burst, src = peaks()
+    out = {"compare": "latent attention (Bebuvik) beside dense GQA (Qwen3) at equal layer sizes", "layers": COMPARE_LAYERS,
+           "vocab": COMPARE_VOCAB, "prompt": COMPARE_PROMPT, "decode_batch": COMPARE_BATCH, "peaks": src, "sizes": {}}
+    every = ("gemm", "attention", "norm", "rope", "other")
+    for size in (args.compare_sizes.split(",") if args.compare_sizes else list(COMPARE_SIZES)):
+        rows = {}
+        for entry in compare_entries(size):
+            args.batch = COMPARE_BATCH
+            bench = Bench(args, entry)
+            a, T = bench.arith, bench.prompt_len
+            head = bench.decode_rate(COMPARE_BATCH, args.steps, args.warmup)
+            pre_ms = bench.prefill_ms()
+            flops = a["gemm_flops"](T) + a["attn_flops"](T)
+            step_bytes = a["weight_bytes"] + COMPARE_BATCH * min(head["ctx_mid"], 4096) * a["kv_bytes_per_token"]
+            print(f"[compare] {entry['name']}: decode {head['ms']:.3f} ms a step, prefill {pre_ms:.3f} ms", file=sys.stderr, flush=True)
+            row = {"decode_tokens_per_s": round(head["rate"], 1), "decode_ms": round(head["ms"], 4), "decode_launches_per_step": head["launches"] // args.steps,
+                   "decode_frac_hbm": round(step_bytes / (head["ms"] * 1e-3) / 1e9 / hbm, 3),
+                   "prefill_tokens_per_s": round(T / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
+                   "prefill_frac_burst": round(flops / (pre_ms * 1e-3) / 1e12 / burst, 3), "weight_gb": round(a["weight_bytes"] / 1e9, 3), "classes": {}}
+            work = {"gemm": (a["weight_bytes"], a["gemm_flops"](T)),
+                    "attention": (COMPARE_BATCH * min(head["ctx_mid"], 4096) * a["kv_bytes_per_token"], a["attn_flops"](T))}
+            def timed(knocked):
+                kernels.knock_out = frozenset(knocked)
+                bench.engine._graphs.clear()
+                try:
+                    return bench.decode_rate(COMPARE_BATCH, 16, 3)["ms"], bench.prefill_ms(runs=3, warm=1)
+                finally:
+                    kernels.knock_out = frozenset()
+                    bench.engine._graphs.clear()
+
+            rest = [head["ms"], pre_ms]
+            for cls in ("gemm", "attention"):      # the two classes with a roofline of their own; the others are `rest`
+                d_alone, _ = timed([c for c in every if c != cls])
+                _, p_without = timed([cls])
+                c = {"decode_alone_ms": round(d_alone, 4), "prefill_left_out_ms": round(pre_ms - p_without, 4)}
+                if d_alone > 0 and pre_ms > p_without:
+                    c["decode_frac_hbm"] = round(work[cls][0] / (d_alone * 1e-3) / 1e9 / hbm, 3)
+                    c["prefill_frac_burst"] = round(work[cls][1] / ((pre_ms - p_without) * 1e-3) / 1e12 / burst, 3)
+                rest[0] -= d_alone
+                rest[1] -= pre_ms - p_without
+                row["classes"][cls] = c
+                print(f"[compare] {entry['name']} {cls}: {c}", file=sys.stderr, flush=True)
+            row["classes"]["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
+            rows[entry["name"]] = row
+            del bench
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rows
+    return out
+
+
 def mixed_workload(args, entry):
     """The scheduler workload: 32 requests with prompts of 128 to 4,096 tokens (seeded), 128 new tokens each at
     temperature 0.7 in a context of 8,192, all submitted at once through Model.generate_batch. The first pass
@@ -549,6 +664,9 @@ def main() -> int:
                     help="run one part only (for profiler captures of a small case)")
     ap.add_argument("--timeline", action="store_true",
                     help="build the kernels with their time stamps and print where a decode step's time goes, kernel by kernel")
+    ap.add_argument("--compare", action="store_true",
+                    help="instead of the headline workload: latent-attention layers beside dense GQA layers of equal sizes")
+    ap.add_argument("--compare-sizes", default=None, help="widths to compare, with commas between them (default: all)")
     args = ap.parse_args()
     if args.timeline:
         os.environ["QUANTINFER_B200_TIMELINE"] = "1"      # before the library is built and loaded
@@ -572,6 +690,10 @@ def main() -> int:
     from quantinfer_b200 import Model
 
     torch.cuda.set_device(0)
+    if args.compare:
+        args.skip_points = args.skip_classes = True
+        print(json.dumps(compare_designs(args)))
+        return 0
     if args.only == "mixed":
         print(json.dumps({"only": "mixed", "mixed": mixed_workload(args, entry)}))
         return 0

@@ -74,7 +74,7 @@ namespace {
 
 template <typename T, int ACT>
 __global__ void activation_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
         out[idx] = qi::from_f32<T>(act<ACT>(qi::to_f32<T>(in[idx])));
 }
@@ -84,7 +84,7 @@ template <typename TG, typename TY>
 __global__ void gated_sum_kernel(const TG* __restrict__ gates, int ldg, const float* __restrict__ b0,
                                  const float* __restrict__ b1, const TY* __restrict__ y0, const TY* __restrict__ y1,
                                  float* __restrict__ out, int n_tokens, int C) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     const size_t total = (size_t)n_tokens * C;
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / C, c = idx % C;
@@ -96,7 +96,7 @@ __global__ void gated_sum_kernel(const TG* __restrict__ gates, int ldg, const fl
 }
 
 __global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x)
         x[idx] = cap * tanhf(x[idx] * inv_cap);
 }

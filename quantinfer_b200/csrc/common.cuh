@@ -72,6 +72,7 @@ __device__ __forceinline__ void pdl_enter() {
     pdl_launch_dependents();
     pdl_wait();
 }
+// A kernel that calls pdl_wait() alone may itself start early, but keeps its successor out until it has ended.
 
 bool pdl_enabled();   // host: false when QUANTINFER_B200_PDL=0
 

@@ -57,7 +57,7 @@ __global__ void embedding_bigram_kernel(const TW* __restrict__ table, const TW* 
                                         float* __restrict__ out, int hidden, int vocab, long long buckets,
                                         long long mul_prev, long long mul_cur, int* __restrict__ status) {
     __shared__ long long s_row;
-    qi::pdl_enter();
+    qi::pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     if (threadIdx.x == 0) {

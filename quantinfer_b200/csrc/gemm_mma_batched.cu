@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128)
 gemm_mma_batched_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y, int M, int N, int K,
                         long long ldx, long long ldw, long long ldy, long long sx, long long sw, long long sy) {
     __shared__ __align__(128) unsigned char smem[2 * (BM + BN) * kStride];
-    qi::pdl_enter();
+    qi::pdl_wait();
     x += (size_t)blockIdx.z * sx;
     w += (size_t)blockIdx.z * sw;
     y += (size_t)blockIdx.z * sy;

@@ -38,7 +38,7 @@ latent_prepare_kernel(const TP* __restrict__ proj, long long ldp, int kv_off, T*
     float* cs = smem;                 // [rot_dims / 2]
     float* sn = smem + rot_dims / 2;  // [rot_dims / 2]
     float* scratch = sn + rot_dims / 2;   // [32]
-    qi::pdl_enter();
+    qi::pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     for (int i = threadIdx.x; i < rot_dims / 2; i += blockDim.x) {
@@ -111,7 +111,7 @@ latent_attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, co
     float* part_m = part_acc + kWarps * R;      // [kWarps]
     float* part_l = part_m + kWarps;            // [kWarps]
 
-    qi::pdl_enter();
+    qi::pdl_wait();
     const int t = blockIdx.y, h = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int pos = positions[t];

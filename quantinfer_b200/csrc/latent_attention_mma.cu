@@ -12,8 +12,10 @@
 // holds its tile, so a launch needs no host-side list and can be replayed from a CUDA graph; the grid is an
 // upper bound (tokens / tokens-per-tile + entries) and the CTAs beyond the last tile leave at once.
 //
-// Key tiles of 64 positions start at multiples of 64 of the absolute position, whatever the portion: the
-// sums of a query row are formed in the same order however the prompt was cut. Rows of the tile outside
+// Key tiles of 64 positions (32 for rows wider than 192, so that two CTAs share an SM) start at multiples of
+// their size in the absolute position, whatever the portion: the sums of a query row are formed in the same
+// order however the prompt was cut. A step of few query tiles and many keys (decode) spreads every tile's key
+// tiles over grid.z; the ranges' partial sums meet in a second kernel, which also adds the sink. Rows of the tile outside
 // [first visible key, last query] are zero-filled and never looked up (their pages may be free again behind
 // a window); each score is masked by its own row's causal bound and window. The softmax's denominator
 // takes exp(sink_h) once, at the end. Key tiles are double-buffered with cp.async; rows are padded by 16
@@ -27,8 +29,6 @@ using qi::bf16;
 
 constexpr int kRows = 64;
 constexpr int kThreads = 128;
-constexpr int KT = 64;
-constexpr int NT = KT / 8;
 
 template <int W> struct PadRows {
     static constexpr int kStride = W * 2 + 16;
@@ -44,38 +44,52 @@ __device__ __forceinline__ void st_zero16(uint32_t dst) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
 }
 
-template <int W, int R>
+template <int W, int R, int KT>
 __global__ void __launch_bounds__(kThreads)
 latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
                             const float* __restrict__ sink, const int* __restrict__ block_table, int max_blocks,
                             int page_size, int num_pages, const int* __restrict__ q_start,
                             const int* __restrict__ start_pos, int n_requests, int H, float scale_log2, int window,
-                            int* __restrict__ status) {
+                            int n_splits, float* __restrict__ ws_o, float* __restrict__ ws_ml, int* __restrict__ status) {
     using Addr = PadRows<W>;
     constexpr int kChunks = W / 8;
+    constexpr int NT = KT / 8;
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_entry, s_t0;
     const uint32_t q_s = smem_u32(smem);
     const uint32_t k_s = q_s + kRows * Addr::kStride;
     constexpr uint32_t kTileBytes = KT * Addr::kStride;
 
-    qi::pdl_enter();
+    qi::pdl_wait();
     const int rpt = H < kRows ? H : kRows;      // rows of a tile per token
     const int TQ = kRows / rpt;                 // tokens of a tile
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        // warp 0 walks the entries 32 at a time: each lane one entry's tile count, a prefix sum over the lanes
+        const int lane = threadIdx.x;
         int c = blockIdx.x, found = -1, t0 = 0;
-        for (int e = 0; e < n_requests; ++e) {
-            const int a = q_start[e], len = q_start[e + 1] - a;
-            const int nt = (len + TQ - 1) / TQ;
-            if (c < nt) {
-                found = e;
-                t0 = a + c * TQ;
-                break;
+        for (int e0 = 0; e0 < n_requests && found < 0; e0 += 32) {
+            const int e = e0 + lane;
+            const int a = e < n_requests ? q_start[e] : 0;
+            const int nt = e < n_requests ? (q_start[e + 1] - a + TQ - 1) / TQ : 0;
+            int incl = nt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
             }
-            c -= nt;
+            const unsigned hit = __ballot_sync(0xffffffffu, c < incl);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                found = e0 + src;
+                t0 = __shfl_sync(0xffffffffu, a, src) + (c - __shfl_sync(0xffffffffu, incl - nt, src)) * TQ;
+            } else {
+                c -= __shfl_sync(0xffffffffu, incl, 31);
+            }
         }
-        s_entry = found;
-        s_t0 = t0;
+        if (lane == 0) {
+            s_entry = found;
+            s_t0 = t0;
+        }
     }
     __syncthreads();
     const int e = s_entry, t0 = s_t0;
@@ -88,6 +102,24 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     const int key_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
     const int* table = block_table + (size_t)e * max_blocks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_begin = key_lo / KT * KT;
+    const int n_tiles = (p_hi - k_begin) / KT + 1;
+    // with key ranges (grid.z, a decode step): this CTA's share of the key tiles; its rows' partial sums go to the
+    // workspace and a second kernel adds the ranges. A range without tiles leaves empty partial sums.
+    int it0 = 0, it1 = n_tiles;
+    if (n_splits > 1) {
+        const int per = (n_tiles + n_splits - 1) / n_splits;
+        it0 = blockIdx.z * per;
+        it1 = min(n_tiles, it0 + per);
+        if (it0 >= it1) {
+            for (int rho = threadIdx.x; rho < nvalid; rho += kThreads) {
+                float* ml = ws_ml + (((size_t)t0 * H + h0 + rho) * n_splits + blockIdx.z) * 2;
+                ml[0] = -INFINITY;
+                ml[1] = 0.f;
+            }
+            return;
+        }
+    }
 
     // the query rows: contiguous in memory from row t0 * H + h0
     const bf16* q_rows = q + ((size_t)t0 * H + h0) * W;
@@ -114,9 +146,7 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
             else st_zero16(dst);
         }
     };
-    const int k_begin = key_lo / KT * KT;
-    const int n_tiles = (p_hi - k_begin) / KT + 1;
-    load_keys(k_begin, 0);
+    load_keys(k_begin + it0 * KT, 0);
     cp_commit();
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -136,14 +166,14 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
         lo_row[r] = window > 0 ? p_row[r] - window + 1 : 0;
     }
 
-    for (int it = 0; it < n_tiles; ++it) {
+    for (int it = it0; it < it1; ++it) {
         const int k0 = k_begin + it * KT;
-        if (it + 1 < n_tiles) load_keys(k0 + KT, (it + 1) & 1);
+        if (it + 1 < it1) load_keys(k0 + KT, (it - it0 + 1) & 1);
         cp_commit();
         cp_wait<1>();
         __syncthreads();
         if (active) {
-            const uint32_t kt = k_s + (it & 1) * kTileBytes;
+            const uint32_t kt = k_s + ((it - it0) & 1) * kTileBytes;
             float s[NT][4];
 #pragma unroll
             for (int j = 0; j < NT; ++j)
@@ -184,6 +214,17 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         if (rho >= nvalid) continue;
+        if (n_splits > 1) {
+            const size_t slot = ((size_t)t0 * H + h0 + rho) * n_splits + blockIdx.z;
+            if ((lane & 3) == 0) {
+                ws_ml[slot * 2] = m[r];
+                ws_ml[slot * 2 + 1] = sum;
+            }
+            float* po = ws_o + slot * R + (lane & 3) * 2;
+#pragma unroll
+            for (int n = 0; n < R / 8; ++n) *reinterpret_cast<float2*>(po + n * 8) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+            continue;
+        }
         const int h = h0 + rho % rpt;
         const float sk = sink ? sink[h] * 1.4426950408889634f : -INFINITY;
         const float mf = fmaxf(m[r], sk);
@@ -197,14 +238,52 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
     }
 }
 
+// Adds the key ranges of a row: out = sum_i o_i 2^(m_i - M) / (sum_i l_i 2^(m_i - M) + 2^(sink - M)), M the largest of
+// the ranges' maxima and the sink (all in the base-2 scale of the main kernel).
+template <int R>
+__global__ void latent_attention_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
+                                              const float* __restrict__ sink, bf16* __restrict__ out, int H, int n_splits) {
+    extern __shared__ float wgt[];      // [n_splits]: 2^(m_i - M) / denominator, 0 for an empty range
+    __shared__ float s_red[2];
+    qi::pdl_wait();
+    const size_t row = blockIdx.x;
+    const float sk = sink ? sink[row % H] * 1.4426950408889634f : -INFINITY;
+    if (threadIdx.x < 32) {
+        // one warp: lane i takes ranges i, i + 32, ...; their loads are in flight together
+        const int lane = threadIdx.x;
+        float M = sk;
+        for (int i = lane; i < n_splits; i += 32) M = fmaxf(M, ws_ml[(row * n_splits + i) * 2]);
+        M = qi::warp_max(M);
+        float denom = 0.f;
+        for (int i = lane; i < n_splits; i += 32) {
+            const float mi = ws_ml[(row * n_splits + i) * 2];
+            const float f = mi == -INFINITY ? 0.f : ex2(mi - M);
+            wgt[i] = f;
+            denom += f * ws_ml[(row * n_splits + i) * 2 + 1];
+        }
+        denom = qi::warp_sum(denom) + (sink ? ex2(sk - M) : 0.f);
+        if (lane == 0) s_red[0] = denom > 0.f ? 1.0f / denom : 0.f;
+    }
+    __syncthreads();
+    const float inv = s_red[0];
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float acc = 0.f;
+#pragma unroll 4
+        for (int i = 0; i < n_splits; ++i)
+            if (wgt[i] != 0.f) acc = fmaf(ws_o[(row * n_splits + i) * R + c], wgt[i], acc);   // an empty range wrote no sums
+        out[row * R + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int W, int R>
 int launch_mma(const void* q, void* out, const void* cache, const float* sink, const int* block_table, int max_blocks,
                int page_size, int num_pages, const int* q_start, const int* start_pos, int n_requests, int n_tokens, int H,
-               float scale, int window, int* status, cudaStream_t stream) {
+               float scale, int window, int n_splits, float* ws_o, float* ws_ml, int* status, cudaStream_t stream) {
+    constexpr int KT = W > 192 ? 32 : 64;      // wide rows: shorter key tiles, so that two CTAs share an SM
     const size_t smem = (size_t)(kRows + 2 * KT) * PadRows<W>::kStride;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(latent_attention_mma_kernel<W, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(latent_attention_mma_kernel<W, R, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return qi::fail("latent_attention_mma: %zu bytes of shared memory were refused", smem);
         configured = true;
     }
@@ -212,10 +291,13 @@ int launch_mma(const void* q, void* out, const void* cache, const float* sink, c
     const int TQ = kRows / rpt;
     const long long tiles = (long long)n_tokens / TQ + n_requests;
     QI_REQUIRE(tiles <= 0x7fffffffll, "latent_attention_mma: grid too large");
-    dim3 grid((unsigned)tiles, (unsigned)((H + kRows - 1) / kRows));
-    qi::launch(latent_attention_mma_kernel<W, R>, grid, dim3(kThreads), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)cache, sink,
+    dim3 grid((unsigned)tiles, (unsigned)((H + kRows - 1) / kRows), (unsigned)n_splits);
+    qi::launch(latent_attention_mma_kernel<W, R, KT>, grid, dim3(kThreads), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)cache, sink,
                block_table, max_blocks, page_size, num_pages, q_start, start_pos, n_requests, H, scale * 1.4426950408889634f, window,
-               status);
+               n_splits, ws_o, ws_ml, status);
+    if (n_splits > 1)
+        qi::launch(latent_attention_merge_kernel<R>, dim3((unsigned)((size_t)n_tokens * H)), dim3(R >= 128 ? 128 : 64), sizeof(float) * n_splits, stream,
+                   (const float*)ws_o, (const float*)ws_ml, sink, (bf16*)out, H, n_splits);
     return qi::check_launch("latent_attention_mma");
 }
 
@@ -227,13 +309,20 @@ extern "C" int qi_latent_attention_mma_supported(int W, int R) {
     return (R == 32 || R == 64 || R == 128 || R == 256) && (r == 16 || r == 32 || r == 64);
 }
 
+// Key tiles of a query tile per CTA: 64 keys, or 32 for rows wider than 192.
+extern "C" int qi_latent_attention_mma_key_tile(int W) { return W > 192 ? 32 : 64; }
+
+// n_splits > 1 cuts every query tile's keys into that many ranges over grid.z (for steps of few query tiles and many
+// keys: decode); ws_o float32 [n * H, n_splits, R] and ws_ml float32 [n * H, n_splits, 2] then take the partial sums.
 // q [n, H, W], out [n, H, R], cache [num_pages, page_size, W], all bfloat16; sink float32 [H] or null; q_start
 // [n_requests + 1] and start_pos [n_requests] as in the step's arrays (entry e's rows are q_start[e] ..
 // q_start[e + 1] - 1 at positions start_pos[e] ...).
 extern "C" int qi_latent_attention_mma(const void* q, void* out, const void* cache, const float* sink, const int* block_table,
                                        int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
-                                       int n_requests, int n_tokens, int H, int W, int R, float scale, int window, int* status,
-                                       cudaStream_t stream) {
+                                       int n_requests, int n_tokens, int H, int W, int R, float scale, int window, int n_splits,
+                                       float* ws_o, float* ws_ml, int* status, cudaStream_t stream) {
+    QI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || (ws_o && ws_ml)), "latent_attention_mma: bad key ranges or no workspace for them");
+    QI_REQUIRE((long long)n_tokens * H <= 0x7fffffffll, "latent_attention_mma: too many rows");
     QI_REQUIRE(qi_latent_attention_mma_supported(W, R), "latent_attention_mma: a latent of %d with a rotated part of %d is not covered", R, W - R);
     QI_REQUIRE(n_tokens >= 0 && n_requests >= 0 && H > 0 && H <= 65535 * kRows, "latent_attention_mma: bad sizes");
     QI_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "latent_attention_mma: bad page geometry or window");
@@ -241,7 +330,7 @@ extern "C" int qi_latent_attention_mma(const void* q, void* out, const void* cac
 #define QI_LATENT_CASE(RR, rr)                                                                                               \
     if (R == RR && W - R == rr)                                                                                              \
         return launch_mma<RR + rr, RR>(q, out, cache, sink, block_table, max_blocks, page_size, num_pages, q_start, start_pos, \
-                                       n_requests, n_tokens, H, scale, window, status, stream);
+                                       n_requests, n_tokens, H, scale, window, n_splits, ws_o, ws_ml, status, stream);
     QI_LATENT_CASE(32, 16) QI_LATENT_CASE(32, 32) QI_LATENT_CASE(32, 64)
     QI_LATENT_CASE(64, 16) QI_LATENT_CASE(64, 32) QI_LATENT_CASE(64, 64)
     QI_LATENT_CASE(128, 16) QI_LATENT_CASE(128, 32) QI_LATENT_CASE(128, 64)

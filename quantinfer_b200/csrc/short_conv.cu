@@ -29,7 +29,7 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
                   const int* __restrict__ token_req, const int* __restrict__ q_start,
                   const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
                   int taps, int n_filters, int residual) {
-    qi::pdl_enter();
+    qi::pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tokens * C) return;
     const int t = (int)(idx / C), c = (int)(idx % C);

@@ -923,11 +923,19 @@ def latent_attention_mma_supported(W: int, R: int) -> bool:
     return bool(library().qi_latent_attention_mma_supported(W, R))
 
 
+def latent_attention_ranges(n_tiles: int, max_keys: int, W: int) -> int:
+    """Into how many key ranges the tensor-core latent attention cuts every query tile: as many as fill the CTAs
+    that are resident at once (two on each of 148 SMs), at most one per key tile."""
+    key_tile = library().qi_latent_attention_mma_key_tile(W)
+    return max(1, min(-(-max_keys // key_tile), 296 // max(n_tiles, 1), 128))
+
+
 def latent_attention(q, out, cache, sink, block_table, q_start, start_pos, positions, token_req, scale: float, window: int,
-                     status, impl: str | None = None) -> None:
+                     status, impl: str | None = None, key_ranges: int = 1) -> None:
     """`latent_attention_generic`'s result by the kernel that fits: "mma" (bfloat16, latent widths the tensor-core
     kernel covers: flash form, one key tile for all heads) or "generic". `q_start`, `start_pos`: the step's per-entry
-    arrays (the tensor-core kernel finds its query tiles from them on the device)."""
+    arrays (the tensor-core kernel finds its query tiles from them on the device). `key_ranges` > 1 spreads every
+    query tile's keys over that many CTAs and adds their partial sums in a second kernel (decode steps)."""
     n, heads, W = q.shape
     R = out.shape[2]
     if impl is None:
@@ -947,7 +955,11 @@ def latent_attention(q, out, cache, sink, block_table, q_start, start_pos, posit
         _req(sink, "sink", torch.float32, 1)
         if sink.numel() != heads:
             raise KernelError("latent_attention: one sink a head")
+    ws_o = ws_ml = None
+    if key_ranges > 1:
+        ws_o = torch.empty((n * heads, key_ranges, R), dtype=torch.float32, device=q.device)
+        ws_ml = torch.empty((n * heads, key_ranges, 2), dtype=torch.float32, device=q.device)
     _call("attention", "latent_attention_mma", library().qi_latent_attention_mma,
           _ptr(q), _ptr(out), _ptr(cache), _ptr(sink), _ptr(block_table), block_table.shape[1], cache.shape[1], cache.shape[0],
-          _ptr(q_start), _ptr(start_pos), start_pos.numel(), n, heads, W, R, C.c_float(scale), int(window or 0), _ptr(status),
-          _stream())
+          _ptr(q_start), _ptr(start_pos), start_pos.numel(), n, heads, W, R, C.c_float(scale), int(window or 0), key_ranges,
+          _ptr(ws_o), _ptr(ws_ml), _ptr(status), _stream())

@@ -100,8 +100,14 @@ class LatentAttention(Part):
                                batch.positions, batch.token_req, table, cache.k_pages, self.H, self.d, self.r, self.R, rt.status)
         kernels.head_linear(z, self.d + self.r, 0, self.d, self.uk_t, q.view(n, self.H * W), W, 0)    # q[:, h, :R] = Wuk_h^T q_h
         o_lat = torch.empty((n, self.H, self.R), dtype=x.dtype, device=x.device)
+        ranges = 1
+        if batch.all_decode and x.dtype == torch.bfloat16:
+            # few query tiles, many keys: the keys of every token are spread over CTAs (a bound on the keys, not the
+            # requests' lengths, so that a captured step serves its whole context bucket)
+            keys = min(s.window or batch.max_kv_len, batch.max_kv_len)
+            ranges = kernels.latent_attention_ranges(n * -(-self.H // 64), keys, W)
         kernels.latent_attention(q, o_lat, cache.k_pages, self.sink, table, batch.q_start, batch.start_pos, batch.positions,
-                                 batch.token_req, s.scale, s.window or 0, rt.status)
+                                 batch.token_req, s.scale, s.window or 0, rt.status, key_ranges=ranges)
         o = torch.empty((n, self.H, self.e), dtype=x.dtype, device=x.device)
         kernels.head_linear(o_lat.view(n, self.H * self.R), self.R, 0, self.R, self.uv, o.view(n, self.H * self.e), self.e, 0)
         return self.o(o.view(n, self.H * self.e))                               # o_h = Wuv_h (sum_j p_j c_j), then Wo

@@ -237,13 +237,13 @@ def test_tensor_core_latent_attention_against_float64(R, r, H, window, page):
     q_start, token_req, positions, start_pos, _ = _state_batch(lengths, starts, list(range(n_req)))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     outs = {}
-    for impl in ("mma", "generic"):
+    for impl, ranges in (("mma", 1), ("generic", 1), ("mma", 3), ("mma", 16)):       # 16: more key ranges than some rows have tiles
         out = torch.full((n, H, R), 7.0, dtype=torch.bfloat16, device=DEV)
         kernels.latent_attention(q.to(DEV), out, cache.to(DEV), sink.to(DEV), table.to(DEV), q_start, start_pos, positions,
-                                 token_req, scale, window or 0, status, impl=impl)
+                                 token_req, scale, window or 0, status, impl=impl, key_ranges=ranges)
         outs[impl] = out.float().cpu().double()
         err = (outs[impl] - ref).abs().amax(dim=(1, 2))
-        assert float(err.max()) < 0.03, (impl, int(err.argmax()), float(err.max()))
+        assert float(err.max()) < 0.03, (impl, ranges, int(err.argmax()), float(err.max()))
     assert int(status.item()) == 0
     table[4, (starts[4] + 60) // page] = -1                  # a page the long portion needs is missing: flagged, not read
     out = torch.empty((n, H, R), dtype=torch.bfloat16, device=DEV)
