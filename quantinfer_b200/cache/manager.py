@@ -19,9 +19,10 @@ group, cut into pages of `page_size` positions:
   state (`StateNeed` entries, `[num_slots, *shape]`, zeroed at `open`) and
   whatever the engine keeps per request (sampler state).
 * state of fixed size is overwritten by a step, so a failed step cannot give it
-  back the way it gives pages back: `prepare` copies the request's state rows
-  aside (device to device, in stream order) and `rollback` copies them back.
-  A model without such state pays nothing for this.
+  back the way it gives pages back: `prepare` copies the request's state aside
+  (device to device, in stream order: one copy, since all entries' state of a
+  slot lies in one row of bytes) and `rollback` copies it back. A model without
+  such state pays nothing for this.
 
 The bookkeeping is host-side and needs no device: `device=None` builds the
 manager without pools, which is how the scheduler tests drive it.
@@ -119,8 +120,8 @@ class CacheManager:
         self.groups: list[Group] = []
         self._entry_group: dict[int, tuple] = {}     # entry -> (group index, index in group)
         self.states: dict[int, torch.Tensor] = {}    # entry -> [num_slots, *shape]
-        self._state_saved: dict[int, torch.Tensor] = {}   # the rows as they were before the step in flight
         by_need: dict = {}
+        state_entries = []
         for entry, need in enumerate(self.needs):
             if isinstance(need, _PAGED):
                 if need not in by_need:
@@ -130,12 +131,29 @@ class CacheManager:
                 self._entry_group[entry] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(entry)
             elif isinstance(need, StateNeed):
-                if self.device is not None:
-                    self.states[entry] = torch.zeros((max_requests, *need.shape), dtype=need.dtype or dtype,
-                                                     device=self.device)
-                    self._state_saved[entry] = torch.zeros_like(self.states[entry])
+                state_entries.append(entry)
             elif need is not None:
                 raise CacheError(f"cache entry {entry} asks for {need!r}, which the manager does not know")
+        # All state of fixed size lives in ONE row of bytes per slot (each entry at a 16-byte boundary in it), so
+        # that zeroing a slot, saving it before a step and restoring it after a failed one are one copy a
+        # request however many layers keep state. `states[entry]` is a view [num_slots, *shape] into the rows:
+        # its slot stride is the row's, its other dimensions are contiguous.
+        self._state_rows = self._state_rows_saved = None
+        if self.device is not None and state_entries:
+            offsets, row = {}, 0
+            for entry in state_entries:
+                need = self.needs[entry]
+                n = torch.empty((), dtype=need.dtype or dtype).element_size()
+                for s in need.shape:
+                    n *= s
+                offsets[entry] = (row, n)
+                row = (row + n + 15) // 16 * 16
+            self._state_rows = torch.zeros((max_requests, max(row, 16)), dtype=torch.uint8, device=self.device)
+            self._state_rows_saved = torch.zeros_like(self._state_rows)
+            for entry, (off, n) in offsets.items():
+                need = self.needs[entry]
+                flat = self._state_rows[:, off:off + n].view(need.dtype or dtype)
+                self.states[entry] = flat.unflatten(1, tuple(need.shape)) if len(need.shape) != 1 else flat
         if self.device is not None:
             for g in self.groups:
                 k_page, v_page = g.need.pools(page_size)
@@ -183,8 +201,8 @@ class CacheManager:
         slot = self._free_slots.pop()
         rc = RequestCache(request_id, slot, tables=[[] for _ in self.groups])
         self.requests[request_id] = rc
-        for st in self.states.values():
-            st[slot].zero_()
+        if self._state_rows is not None:
+            self._state_rows[slot].zero_()
         return rc
 
     def get(self, request_id) -> RequestCache:
@@ -222,8 +240,8 @@ class CacheManager:
             raise OutOfPages(
                 f"request {request_id!r} needs {need_blocks} pages per group for {end} positions; "
                 f"a pool of {self.num_pages} pages has none left") from None
-        for entry, st in self.states.items():
-            self._state_saved[entry][rc.slot].copy_(st[rc.slot])
+        if self._state_rows is not None:
+            self._state_rows_saved[rc.slot].copy_(self._state_rows[rc.slot])
         rc.pending = n_new
 
     def commit(self, request_id) -> None:
@@ -248,9 +266,8 @@ class CacheManager:
         """Undoes `prepare`: pages beyond the committed length go back, and state of fixed
         size is again what it was before the step."""
         rc = self.get(request_id)
-        if rc.pending:
-            for entry, st in self.states.items():
-                st[rc.slot].copy_(self._state_saved[entry][rc.slot])
+        if rc.pending and self._state_rows is not None:
+            self._state_rows[rc.slot].copy_(self._state_rows_saved[rc.slot])
         keep = -(-rc.length // self.page_size)
         for gi, g in enumerate(self.groups):
             table = rc.tables[gi]

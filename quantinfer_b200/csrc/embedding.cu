@@ -45,7 +45,7 @@ extern "C" int qi_embedding(const void* table, int table_dtype, const int* ids, 
 //     row_t = (id_(t-1) * mul_prev + id_t * mul_cur) mod buckets      for a token that has a predecessor,
 //     row_t = buckets (the table's last row)                          for the first token of a sequence.
 // The predecessor of an entry's first token is the last token of the request's previous step, kept in
-// `prev_state[slot]` (int32, one word a slot). The block of an entry's first token reads that word and
+// `prev_state[slot * state_stride]` (int32, one word a slot). The block of an entry's first token reads that word and
 // then writes the entry's last token into it; no other block touches it, so a step needs no second pass.
 namespace {
 
@@ -55,7 +55,8 @@ __global__ void embedding_bigram_kernel(const TW* __restrict__ table, const TW* 
                                         const int* __restrict__ token_req, const int* __restrict__ q_start,
                                         const int* __restrict__ slot_ids, int* __restrict__ prev_state,
                                         float* __restrict__ out, int hidden, int vocab, long long buckets,
-                                        long long mul_prev, long long mul_cur, int* __restrict__ status) {
+                                        long long mul_prev, long long mul_cur, long long state_stride,
+                                        int* __restrict__ status) {
     __shared__ long long s_row;
     qi::pdl_wait();
     const int t = blockIdx.x;
@@ -65,11 +66,11 @@ __global__ void embedding_bigram_kernel(const TW* __restrict__ table, const TW* 
         const int first = q_start[e], last = q_start[e + 1] - 1;
         long long row = buckets;
         if (positions[t] > 0) {
-            const long long prev = t > first ? ids[t - 1] : prev_state[slot_ids[e]];
+            const long long prev = t > first ? ids[t - 1] : prev_state[(size_t)slot_ids[e] * state_stride];
             row = (prev * mul_prev + (long long)id * mul_cur) % buckets;
             if (row < 0) row += buckets;
         }
-        if (t == first) prev_state[slot_ids[e]] = ids[last];
+        if (t == first) prev_state[(size_t)slot_ids[e] * state_stride] = ids[last];
         s_row = row;
     }
     __syncthreads();
@@ -90,7 +91,8 @@ extern "C" int qi_embedding_bigram(const void* table, const void* bigram, int ta
                                    const int* positions, const int* token_req, const int* q_start,
                                    const int* slot_ids, int* prev_state, float* out, int n_tokens, int hidden,
                                    int vocab, long long buckets, long long mul_prev, long long mul_cur,
-                                   int* status, cudaStream_t stream) {
+                                   long long state_stride, int* status, cudaStream_t stream) {
+    QI_REQUIRE(state_stride >= 1, "embedding_bigram: the state's slot stride must be at least one word");
     QI_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0 && buckets > 0, "embedding_bigram: bad sizes n=%d hidden=%d vocab=%d buckets=%lld",
                n_tokens, hidden, vocab, buckets);
     QI_REQUIRE(mul_prev >= 0 && mul_cur >= 0 && mul_prev < (1ll << 31) && mul_cur < (1ll << 31), "embedding_bigram: multipliers must fit 31 bits");
@@ -98,7 +100,7 @@ extern "C" int qi_embedding_bigram(const void* table, const void* bigram, int ta
     const int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
     QI_DISPATCH_DTYPE(table_dtype, TW, {
         qi::launch(embedding_bigram_kernel<TW>, dim3(n_tokens), dim3(threads), 0, stream, (const TW*)table, (const TW*)bigram, ids,
-                   positions, token_req, q_start, slot_ids, prev_state, out, hidden, vocab, buckets, mul_prev, mul_cur, status);
+                   positions, token_req, q_start, slot_ids, prev_state, out, hidden, vocab, buckets, mul_prev, mul_cur, state_stride, status);
     });
     return qi::check_launch("embedding_bigram");
 }

@@ -81,7 +81,9 @@ latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, 
             if (hit) {
                 const int src = __ffs(hit) - 1;
                 found = e0 + src;
-                t0 = __shfl_sync(0xffffffffu, a, src) + (c - __shfl_sync(0xffffffffu, incl - nt, src)) * TQ;
+                // an entry's tiles from its end: the tiles with the most keys start first, the short ones fill the tail
+                const int within = c - __shfl_sync(0xffffffffu, incl - nt, src);
+                t0 = __shfl_sync(0xffffffffu, a, src) + (__shfl_sync(0xffffffffu, nt, src) - 1 - within) * TQ;
             } else {
                 c -= __shfl_sync(0xffffffffu, incl, 31);
             }

@@ -28,7 +28,7 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
                   TO* __restrict__ out0, TO* __restrict__ out1, TO* __restrict__ copy,
                   const int* __restrict__ token_req, const int* __restrict__ q_start,
                   const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
-                  int taps, int n_filters, int residual) {
+                  int taps, int n_filters, int residual, long long state_stride) {
     qi::pdl_wait();
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_tokens * C) return;
@@ -55,7 +55,7 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
     // the entry's first token: old state in registers, the first rows, then the new state
     const int len = q_start[e + 1] - first;
     const int p0 = start_pos[e];
-    float* st = state + (size_t)slot_ids[e] * back * C + c;
+    float* st = state + (size_t)slot_ids[e] * state_stride + c;
     float old[kMaxTaps];
 #pragma unroll
     for (int k = 0; k < kMaxTaps; ++k) old[k] = 0.f;
@@ -96,12 +96,13 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
 
 }  // namespace
 
-// h float32 [n_tokens, C]; w float32 [n_filters, taps, C]; state float32 [slots, taps - 1, C] (may be null when
-// taps == 1); out0, out1 (out1 only with two filters) and copy (may be null) [n_tokens, C] in `out_dtype`.
+// h float32 [n_tokens, C]; w float32 [n_filters, taps, C]; state float32 [slots, taps - 1, C] with `state_stride`
+// floats from slot to slot (at least (taps - 1) * C; may be null when taps == 1); out0, out1 (out1 only with two filters) and copy (may be null) [n_tokens, C] in `out_dtype`.
 extern "C" int qi_short_conv(const float* h, const float* w, float* state, void* out0, void* out1, void* copy,
                              int out_dtype, const int* token_req, const int* q_start, const int* start_pos,
                              const int* slot_ids, int n_tokens, int channels, int taps, int n_filters, int residual,
-                             cudaStream_t stream) {
+                             long long state_stride, cudaStream_t stream) {
+    QI_REQUIRE(taps == 1 || state_stride >= (long long)(taps - 1) * channels, "short_conv: the slots of the state overlap");
     QI_REQUIRE(n_tokens >= 0 && channels > 0, "short_conv: bad sizes n=%d channels=%d", n_tokens, channels);
     QI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "short_conv: %d taps are outside 1..%d", taps, kMaxTaps);
     QI_REQUIRE(n_filters == 1 || n_filters == 2, "short_conv: one or two filters a launch, got %d", n_filters);
@@ -112,7 +113,7 @@ extern "C" int qi_short_conv(const float* h, const float* w, float* state, void*
     QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "short_conv: grid too large");
     QI_DISPATCH_DTYPE(out_dtype, TO, {
         qi::launch(short_conv_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, h, w, state, (TO*)out0, (TO*)out1,
-                   (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps, n_filters, residual);
+                   (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps, n_filters, residual, state_stride);
     });
     return qi::check_launch("short_conv");
 }

@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 
 def status_names(code: int) -> list:
@@ -128,6 +128,15 @@ def _req(t: torch.Tensor, name: str, dtype=None, ndim=None) -> None:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
     if ndim is not None and t.dim() != ndim:
         raise KernelError(f"{name} must have {ndim} dimensions, got shape {tuple(t.shape)}")
+
+
+def _req_state(t: torch.Tensor, name: str, dtype) -> None:
+    """State of fixed size [slots, ...]: the slots may lie apart (rows of the cache manager's state memory), what
+    a slot holds must be contiguous."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != dtype or t.dim() < 2:
+        raise KernelError(f"{name} must be a CUDA tensor of {dtype} with a slot dimension")
+    if not t[0].is_contiguous() or t.stride(0) < t[0].numel():
+        raise KernelError(f"{name}: what a slot holds must be contiguous and the slots must not overlap")
 
 
 def _ptr(t) -> C.c_void_p:
@@ -755,8 +764,9 @@ def embedding_bigram(table, bigram, ids, positions, token_req, q_start, slot_ids
     _req(bigram, "bigram", table.dtype, 2)
     _req(out, "out", torch.float32, 2)
     for t, name in ((ids, "ids"), (positions, "positions"), (token_req, "token_req"), (q_start, "q_start"),
-                    (slot_ids, "slot_ids"), (prev_state, "prev_state")):
+                    (slot_ids, "slot_ids")):
         _req(t, name, torch.int32)
+    _req_state(prev_state, "prev_state", torch.int32)
     n, hidden = out.shape
     if ids.numel() != n or table.shape[1] != hidden or tuple(bigram.shape) != (buckets + 1, hidden):
         raise KernelError(f"embedding_bigram: shapes do not agree: table {tuple(table.shape)}, bigram {tuple(bigram.shape)} "
@@ -764,7 +774,7 @@ def embedding_bigram(table, bigram, ids, positions, token_req, q_start, slot_ids
     _call("other", "embedding_bigram", library().qi_embedding_bigram,
           _ptr(table), _ptr(bigram), _code(table), _ptr(ids), _ptr(positions), _ptr(token_req), _ptr(q_start),
           _ptr(slot_ids), _ptr(prev_state), _ptr(out), n, hidden, table.shape[0], C.c_longlong(buckets),
-          C.c_longlong(mul_prev), C.c_longlong(mul_cur), _ptr(status), _stream())
+          C.c_longlong(mul_prev), C.c_longlong(mul_cur), C.c_longlong(prev_state.stride(0)), _ptr(status), _stream())
 
 
 def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slot_ids, residual: bool = True) -> None:
@@ -783,7 +793,7 @@ def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slo
         if tuple(o.shape) != (n, ch):
             raise KernelError(f"short_conv: an output is {tuple(o.shape)}, expected {(n, ch)}")
     if taps > 1:
-        _req(state, "state", torch.float32, 3)
+        _req_state(state, "state", torch.float32)
         if tuple(state.shape[1:]) != (taps - 1, ch):
             raise KernelError(f"short_conv: state {tuple(state.shape)} does not fit {taps} taps of {ch} channels")
     for t, name in ((token_req, "token_req"), (q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
@@ -791,7 +801,7 @@ def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slo
     _call("other", "short_conv", library().qi_short_conv,
           _ptr(h), _ptr(weights), _ptr(state if taps > 1 else None), _ptr(outs[0]), _ptr(outs[1] if filters > 1 else None),
           _ptr(copy), _code(outs[0]), _ptr(token_req), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), n, ch, taps, filters,
-          int(bool(residual)), _stream())
+          int(bool(residual)), C.c_longlong(state.stride(0) if taps > 1 else 0), _stream())
 
 
 def head_linear(x, x_head_width: int, x_offset: int, k: int, w, out, out_head_width: int, out_offset: int) -> None:
