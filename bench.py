@@ -492,12 +492,50 @@ def compare_designs(args):
                 row["classes"][cls] = c
                 print(f"[compare] {entry['name']} {cls}: {c}", file=sys.stderr, flush=True)
             row["classes"]["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
+            alone = latent_attention_kernel(bench.config, T, burst) if hasattr(bench.config, "layers") else bench.prefill_attention_kernel(burst)
+            if alone:
+                row["classes"]["attention"].update(alone)
+                print(f"[compare] {entry['name']} attention kernel alone: {alone}", file=sys.stderr, flush=True)
             rows[entry["name"]] = row
             del bench
             gc.collect()
             torch.cuda.empty_cache()
         out["sizes"][size] = rows
     return out
+
+
+def latent_attention_kernel(config, T, burst):
+    """The latent attention's prefill kernel by itself at the first layer's sizes: one prompt of T tokens, 20 launches
+    back to back between two events."""
+    import torch
+
+    from quantinfer_b200 import kernels
+
+    m = config.layers[0].mixer
+    H, R, W, ps, dev = m.heads, m.kv_rank, m.kv_rank + m.rot_dim, 64, "cuda:0"
+    if not kernels.latent_attention_mma_supported(W, R):
+        return None
+    n_pages = T // ps + 1
+    cache = (torch.randn(n_pages, ps, W, device=dev) * 0.5).to(torch.bfloat16)
+    q = (torch.randn(T, H, W, device=dev) * 0.5).to(torch.bfloat16)
+    out = torch.empty(T, H, R, dtype=torch.bfloat16, device=dev)
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(1, -1)
+    positions, token_req = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    args = (q, out, cache, torch.zeros(H, device=dev), table, as_int([0, T]), as_int([0]), positions, token_req, m.scale, m.window or 0, status)
+    for _ in range(3):
+        kernels.latent_attention(*args, impl="mma")
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(20):
+        kernels.latent_attention(*args, impl="mma")
+    b.record()
+    torch.cuda.synchronize()
+    us = a.elapsed_time(b) / 20 * 1e3
+    tf = 2.0 * H * (W + R) * sum(min(t + 1, m.window or T) for t in range(T)) / us / 1e6
+    return {"prefill_kernel_us": round(us, 1), "prefill_kernel_tflops": round(tf, 1), "prefill_kernel_frac_burst": round(tf / burst, 3)}
 
 
 def mixed_workload(args, entry):
