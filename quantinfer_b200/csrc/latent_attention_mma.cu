@@ -2,17 +2,18 @@
 // the flash form of latent_attention.cu for prompts' portions and single decode tokens alike.
 //
 // All heads of a token read the SAME cached rows [c | kr] of width W = R + r, and the value is the row's
-// first R numbers. So the rows of a query tile are (token, head) pairs of one request, 64 of them a CTA
-// (four warps of 16), and one key tile in shared memory serves every head, once as the B operand of
-// S = Q K^T (over W) and once more, read transposed, as the B operand of O += P V (over its first R columns).
-// With H heads a tile holds 64 / H tokens (H <= 64), or 64 of one token's heads (H > 64, the heads then
-// spread over grid.y). A decode token is a tile of H rows.
+// first R numbers. So the rows of a query tile are (token, head) pairs of one request, 16 x MW of them a CTA
+// (MW warps of 16: eight for a step that holds portions of prompts, four for a step of single tokens), and
+// one key tile in shared memory serves every head, once as the B operand of S = Q K^T (over W) and once more,
+// read transposed, as the B operand of O += P V (over its first R columns). With H heads a tile of N rows
+// holds N / H tokens (H <= N), or N of one token's heads (H > N, the heads then spread over grid.y). A decode
+// token is a tile of H rows.
 //
 // Tiles are found on the device: CTA x walks the entries' lengths (q_start) until it meets the entry that
 // holds its tile, so a launch needs no host-side list and can be replayed from a CUDA graph; the grid is an
 // upper bound (tokens / tokens-per-tile + entries) and the CTAs beyond the last tile leave at once.
 //
-// Key tiles of 64 positions (32 for rows wider than 192, so that two CTAs share an SM) start at multiples of
+// Key tiles of 64 positions (32 for rows wider than 192 in CTAs of four warps, so that two share an SM) start at multiples of
 // their size in the absolute position, whatever the portion: the sums of a query row are formed in the same
 // order however the prompt was cut. A step of few query tiles and many keys (decode) spreads every tile's key
 // tiles over grid.z; the ranges' partial sums meet in a second kernel, which also adds the sink. Rows of the tile outside
@@ -27,8 +28,6 @@ namespace {
 using namespace qi_attn;
 using qi::bf16;
 
-constexpr int kRows = 64;
-constexpr int kThreads = 128;
 
 template <int W> struct PadRows {
     static constexpr int kStride = W * 2 + 16;
@@ -44,14 +43,15 @@ __device__ __forceinline__ void st_zero16(uint32_t dst) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0u) : "memory");
 }
 
-template <int W, int R, int KT>
-__global__ void __launch_bounds__(kThreads)
+template <int W, int R, int KT, int MW>
+__global__ void __launch_bounds__(32 * MW)
 latent_attention_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
                             const float* __restrict__ sink, const int* __restrict__ block_table, int max_blocks,
                             int page_size, int num_pages, const int* __restrict__ q_start,
                             const int* __restrict__ start_pos, int n_requests, int H, float scale_log2, int window,
                             int n_splits, float* __restrict__ ws_o, float* __restrict__ ws_ml, int* __restrict__ status) {
     using Addr = PadRows<W>;
+    constexpr int kRows = 16 * MW, kThreads = 32 * MW;      // MW warps of 16 query rows
     constexpr int kChunks = W / 8;
     constexpr int NT = KT / 8;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -277,15 +277,18 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ ws_o, co
     }
 }
 
-template <int W, int R>
+template <int W, int R, int MW>
 int launch_mma(const void* q, void* out, const void* cache, const float* sink, const int* block_table, int max_blocks,
                int page_size, int num_pages, const int* q_start, const int* start_pos, int n_requests, int n_tokens, int H,
                float scale, int window, int n_splits, float* ws_o, float* ws_ml, int* status, cudaStream_t stream) {
-    constexpr int KT = W > 192 ? 32 : 64;      // wide rows: shorter key tiles, so that two CTAs share an SM
+    // wide rows in CTAs of four warps: shorter key tiles, so that two CTAs share an SM (a CTA of eight warps has the
+    // SM to itself by its registers anyway)
+    constexpr int KT = (W > 192 && MW == 4) ? 32 : 64;
+    constexpr int kRows = 16 * MW, kThreads = 32 * MW;
     const size_t smem = (size_t)(kRows + 2 * KT) * PadRows<W>::kStride;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(latent_attention_mma_kernel<W, R, KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(latent_attention_mma_kernel<W, R, KT, MW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return qi::fail("latent_attention_mma: %zu bytes of shared memory were refused", smem);
         configured = true;
     }
@@ -294,7 +297,7 @@ int launch_mma(const void* q, void* out, const void* cache, const float* sink, c
     const long long tiles = (long long)n_tokens / TQ + n_requests;
     QI_REQUIRE(tiles <= 0x7fffffffll, "latent_attention_mma: grid too large");
     dim3 grid((unsigned)tiles, (unsigned)((H + kRows - 1) / kRows), (unsigned)n_splits);
-    qi::launch(latent_attention_mma_kernel<W, R, KT>, grid, dim3(kThreads), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)cache, sink,
+    qi::launch(latent_attention_mma_kernel<W, R, KT, MW>, grid, dim3(kThreads), smem, stream, (const bf16*)q, (bf16*)out, (const bf16*)cache, sink,
                block_table, max_blocks, page_size, num_pages, q_start, start_pos, n_requests, H, scale * 1.4426950408889634f, window,
                n_splits, ws_o, ws_ml, status);
     if (n_splits > 1)
@@ -312,7 +315,7 @@ extern "C" int qi_latent_attention_mma_supported(int W, int R) {
 }
 
 // Key tiles of a query tile per CTA: 64 keys, or 32 for rows wider than 192.
-extern "C" int qi_latent_attention_mma_key_tile(int W) { return W > 192 ? 32 : 64; }
+extern "C" int qi_latent_attention_mma_key_tile(int W) { return W > 192 ? 32 : 64; }      // (of a step of single tokens)
 
 // n_splits > 1 cuts every query tile's keys into that many ranges over grid.z (for steps of few query tiles and many
 // keys: decode); ws_o float32 [n * H, n_splits, R] and ws_ml float32 [n * H, n_splits, 2] then take the partial sums.
@@ -326,13 +329,20 @@ extern "C" int qi_latent_attention_mma(const void* q, void* out, const void* cac
     QI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && (n_splits == 1 || (ws_o && ws_ml)), "latent_attention_mma: bad key ranges or no workspace for them");
     QI_REQUIRE((long long)n_tokens * H <= 0x7fffffffll, "latent_attention_mma: too many rows");
     QI_REQUIRE(qi_latent_attention_mma_supported(W, R), "latent_attention_mma: a latent of %d with a rotated part of %d is not covered", R, W - R);
-    QI_REQUIRE(n_tokens >= 0 && n_requests >= 0 && H > 0 && H <= 65535 * kRows, "latent_attention_mma: bad sizes");
+    QI_REQUIRE(n_tokens >= 0 && n_requests >= 0 && H > 0 && H <= 65535 * 64, "latent_attention_mma: bad sizes");
     QI_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0 && window >= 0, "latent_attention_mma: bad page geometry or window");
     if (n_tokens == 0 || n_requests == 0) return 0;
-#define QI_LATENT_CASE(RR, rr)                                                                                               \
-    if (R == RR && W - R == rr)                                                                                              \
-        return launch_mma<RR + rr, RR>(q, out, cache, sink, block_table, max_blocks, page_size, num_pages, q_start, start_pos, \
-                                       n_requests, n_tokens, H, scale, window, n_splits, ws_o, ws_ml, status, stream);
+    // a step with portions of prompts: CTAs of eight warps (128 rows: more tokens share a key tile, and head counts
+    // that do not divide 64 fill their rows better); a step of single tokens: four warps
+    const bool wide = n_tokens > n_requests;
+#define QI_LATENT_CASE(RR, rr)                                                                                                     \
+    if (R == RR && W - R == rr)                                                                                                    \
+        return wide ? launch_mma<RR + rr, RR, 8>(q, out, cache, sink, block_table, max_blocks, page_size, num_pages, q_start,      \
+                                                 start_pos, n_requests, n_tokens, H, scale, window, n_splits, ws_o, ws_ml, status, \
+                                                 stream)                                                                           \
+                    : launch_mma<RR + rr, RR, 4>(q, out, cache, sink, block_table, max_blocks, page_size, num_pages, q_start,      \
+                                                 start_pos, n_requests, n_tokens, H, scale, window, n_splits, ws_o, ws_ml, status, \
+                                                 stream);
     QI_LATENT_CASE(32, 16) QI_LATENT_CASE(32, 32) QI_LATENT_CASE(32, 64)
     QI_LATENT_CASE(64, 16) QI_LATENT_CASE(64, 32) QI_LATENT_CASE(64, 64)
     QI_LATENT_CASE(128, 16) QI_LATENT_CASE(128, 32) QI_LATENT_CASE(128, 64)
