@@ -427,12 +427,12 @@ COMPARE_LAYERS, COMPARE_VOCAB, COMPARE_PROMPT, COMPARE_BATCH = 4, 32768, 2048, 8
 def compare_entries(size):
     z = COMPARE_SIZES[size]
     mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
-             "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 1000000.0, "dims": z["rot"]}, "mask": {"size": 4096}}
+             "scale": (z["dim"] + z["rot"]) ** -0.5, "rot": {"base": 500000.0, "dims": z["rot"]}, "mask": {"size": 4096}}
     shares = {1: 0, 3: 2}        # every second layer reads the latent of the layer before it
     layers = [{"type": "latent_attention", "mixer": dict(mixer, **({"kv_from": shares[i]} if i in shares else {})),
                "mlp": {"kind": "dense", "ff": z["ff"]}} for i in range(COMPARE_LAYERS)]
     latent = dict(architecture="Bebuvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, canon={"taps": 4},
-                  embedding={"bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 7}}, logit_softcap=30.0, layers=layers)
+                  embedding={"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}}, logit_softcap=30.0, layers=layers)
     dense = dict(_COMMON, vocab_size=COMPARE_VOCAB, hidden_size=z["width"], intermediate_size=(2 * z["ff"] // 3 + 127) // 128 * 128,
                  num_hidden_layers=COMPARE_LAYERS, num_attention_heads=z["heads"], head_dim=z["dim"] + z["rot"])
     common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())

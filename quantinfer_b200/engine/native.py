@@ -82,6 +82,8 @@ class NativeProgram:
 
         if type(model.embedding) is not Embedding or type(model.head) is not LMHead or type(model.final_norm) is not RMSNorm:
             return None
+        if getattr(model.head, "softcap", None) is not None:
+            return None          # the driver's head is the projection alone
         blocks = (_Block * len(model.blocks))()
         for i, b in enumerate(model.blocks):
             if (type(b) is not PreNormBlock or type(b.mixer_norm) is not RMSNorm or type(b.ffn_norm) is not RMSNorm

@@ -38,7 +38,7 @@ CONFIGS = {
     # one head, two taps, a window of one page, sizes that are multiples of 16 (what tensor-core kernels take)
     "Q": {"architecture": "Bebuvik", "vocab": 320, "width": 64, "norm": {"eps": 1e-5}, "canon": {"taps": 2},
           "embedding": {"bigram": {"buckets": 509, "mul_prev": 1, "mul_cur": 3}}, "logit_softcap": 30.0,
-          "layers": [_layer(_mixer(1, 32, 16, 32, 64, window=16, base=1000000.0), 96),
+          "layers": [_layer(_mixer(1, 32, 16, 32, 64, window=16, base=250000.0), 96),
                      _layer(_mixer(4, 16, 16, 16, 32, window=33), 128),
                      _layer(_mixer(8, 16, 16, 32, 32, window=64, kv_from=1), 64)]},
     # what the configuration may leave out: no input convolution, no bigram table, no soft cap, no window
@@ -47,7 +47,7 @@ CONFIGS = {
     # one tap (a filter without state), five taps, long windows over small pages
     "S": {"architecture": "Bebuvik", "vocab": 190, "width": 48, "norm": {"eps": 2e-6}, "canon": {"taps": 5},
           "embedding": {"bigram": {"buckets": 64, "mul_prev": 7, "mul_cur": 7}}, "logit_softcap": 12.0,
-          "layers": [_layer(_mixer(2, 16, 8, 24, 24, window=40), 80), _layer(_mixer(2, 16, 8, 24, 24, window=40, kv_from=0), 80),
+          "layers": [_layer(_mixer(2, 16, 8, 24, 24, window=44), 80), _layer(_mixer(2, 16, 8, 24, 24, window=44, kv_from=0), 80),
                      _layer(_mixer(3, 8, 2, 8, 40, window=7), None)]},
 }
 CONFIGS["T"] = dict(CONFIGS["S"], canon={"taps": 1})

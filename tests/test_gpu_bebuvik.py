@@ -152,8 +152,8 @@ def test_small_kernels_against_their_formulas():
         assert float((act.float().cpu() - plain.gelu_tanh(x.float())).abs().max()) < (2e-6 if dt == torch.float32 else 2e-2)
     z = torch.randn(5, 33) * 40
     zd = z.to(DEV)
-    kernels.softcap(zd, 15.0)
-    assert float((zd.cpu() - 15.0 * torch.tanh(z / 15.0)).abs().max()) < 5e-6
+    kernels.softcap(zd, 11.0)
+    assert float((zd.cpu() - 11.0 * torch.tanh(z / 11.0)).abs().max()) < 5e-6
     # per-head products from rows that hold more than the heads, into rows that hold more too
     heads, xw, k, N, ow = 3, 11, 6, 5, 9
     x, w = torch.randn(n, heads * xw + 4), torch.randn(heads, N, k)
@@ -188,7 +188,7 @@ def test_scalar_norm_and_dense_feed_forward_parts(dtype):
     assert float((y.float().cpu() - ref).abs().max()) < (2e-5 if dtype == torch.float32 else 4e-2)
 
 
-@pytest.mark.parametrize("R, r, H, window, page", [(64, 16, 6, 40, 64), (32, 16, 1, None, 8), (128, 64, 8, 17, 16),
+@pytest.mark.parametrize("R, r, H, window, page", [(64, 16, 5, 37, 64), (32, 16, 1, None, 8), (128, 64, 8, 17, 16),
                                                     (64, 32, 70, 33, 32), (256, 64, 3, 100, 16), (32, 32, 64, 1, 8)])
 def test_tensor_core_latent_attention_against_float64(R, r, H, window, page):
     """The flash kernel alone on a batch of three decode tokens in front of portions of 2, 130 and 37 tokens that
