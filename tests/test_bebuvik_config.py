@@ -144,3 +144,24 @@ def test_the_model_collects_state_entries_for_blocks_and_embedding():
     assert model.cache_needs[2] == StateNeed((2, 44), torch.float32) and model.cache_needs[6] == StateNeed((1,), torch.int32)
     one_tap = Model(config_from_dict(CONFIGS["T"]).to_model_spec(), NoDevice(torch.float32, "cpu"))
     assert one_tap.call_state_entry == [None, None, None]          # a filter of one tap keeps nothing
+
+
+def test_the_comparison_of_bench_py_describes_two_models_of_equal_layer_sizes():
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    from quantinfer_b200.config import config_from_dict
+
+    for size, z in bench.COMPARE_SIZES.items():
+        latent, dense = bench.compare_entries(size)
+        lc, dc = config_from_dict(latent["config"]), config_from_dict(dense["config"])
+        ls, ds = lc.to_model_spec(), dc.to_model_spec()
+        assert (ls.hidden_size, ls.vocab_size, len(ls.layers)) == (ds.hidden_size, ds.vocab_size, len(ds.layers)) == (z["width"], 32768, 4)
+        assert ls.layers[0].mixer.num_heads == ds.layers[0].mixer.num_heads == z["heads"]
+        assert ds.layers[0].mixer.head_dim == z["dim"] + z["rot"]
+        assert [c.writes_cache for c in ls.order] == [True, False, True, False]
+        la, da = bench.model_arithmetic(lc, ls), bench.model_arithmetic(dc, ds)
+        assert 0.8 < la["weight_bytes"] / da["weight_bytes"] < 1.25            # about the same number of parameters
+        assert la["kv_bytes_per_token"] < da["kv_bytes_per_token"] and la["attn_flops"](64) > 0

@@ -25,7 +25,7 @@ DEV = "cuda:0"
 # |engine - plain float64| on logits that the soft cap keeps within a few units. float32: order of sums and the
 # device's exp, tanh, sin, cos. bfloat16: three times the worst error measured per configuration.
 TOL_F32 = 4e-5
-TOL_BF16_MEASURED = {"P": 0.057, "Q": 0.090, "R": 0.035, "S": 0.060, "T": 0.116}
+TOL_BF16_MEASURED = {"P": 0.057, "Q": 0.136, "R": 0.035, "S": 0.081, "T": 0.105}
 LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 150, 5], "R": [50, 33, 80, 17, 64],
            "S": [90, 41, 120, 8, 64, 33], "T": [60, 100, 31, 64, 9, 70]}
 
