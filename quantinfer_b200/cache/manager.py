@@ -189,7 +189,9 @@ class CacheManager:
 
     def live_length(self, group: int, length: int) -> int:
         w = self.groups[group].need.window
-        return length if w is None else min(length, w)
+        c = getattr(self.groups[group].need, "chunk", None)
+        live = length if w is None else min(length, w)
+        return live if not c else min(live, length - (length - 1) // c * c if length else 0)
 
     # ---- requests -------------------------------------------------------
 
@@ -250,11 +252,13 @@ class CacheManager:
         rc.length += rc.pending
         rc.pending = 0
         for gi, g in enumerate(self.groups):
-            w = g.need.window
-            if w is None:
+            w, chunk = g.need.window, getattr(g.need, "chunk", None)
+            if w is None and not chunk:
                 continue
-            # the next query sits at position >= rc.length and reads keys > position - w
-            first_needed = max(0, rc.length - w + 1)
+            # the next query sits at position >= rc.length and reads keys > position - w, and none before its own chunk
+            first_needed = max(0, rc.length - w + 1) if w is not None else 0
+            if chunk:
+                first_needed = max(first_needed, rc.length // chunk * chunk)
             table = rc.tables[gi]
             for b in range(min(first_needed // self.page_size, len(table))):
                 if table[b] >= 0:

@@ -9,23 +9,30 @@ from typing import Optional
 @dataclass(frozen=True)
 class PagedKVNeed:
     """Keys and values of every position (window None) or of the last `window`
-    positions, in pages [num_pages, num_kv_heads, page_size, head_dim]."""
+    positions, in pages [num_pages, num_kv_heads, page_size, head_dim] (values
+    [..., value_dim] when that is given). `chunk`: queries see only the keys of
+    their own chunk of that many positions (counted from the sequence's start),
+    so the pages of earlier chunks go back as soon as a request has passed them."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
-
+    value_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
     def pools(self, page_size: int) -> tuple:
         """Shapes of a page in the key pool and in the value pool."""
-        shape = (self.num_kv_heads, page_size, self.head_dim)
-        return shape, shape
+        return ((self.num_kv_heads, page_size, self.head_dim),
+                (self.num_kv_heads, page_size, self.value_dim or self.head_dim))
 
     def merged(self, other):
         """The need of an entry that `other` reads too, or None when the two cannot share one."""
-        if not isinstance(other, PagedKVNeed) or (other.num_kv_heads, other.head_dim) != (self.num_kv_heads, self.head_dim):
+        if not isinstance(other, PagedKVNeed) or (other.num_kv_heads, other.head_dim, other.value_dim or other.head_dim) != (
+                self.num_kv_heads, self.head_dim, self.value_dim or self.head_dim):
             return None
-        return PagedKVNeed(self.num_kv_heads, self.head_dim, _wider(self.window, other.window))
+        if self.chunk != other.chunk:      # readers with other chunks: keep what any of them may see
+            return PagedKVNeed(self.num_kv_heads, self.head_dim, None, self.value_dim, None)
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, _wider(self.window, other.window), self.value_dim, self.chunk)
 
 
 @dataclass(frozen=True)

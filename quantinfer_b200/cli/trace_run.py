@@ -16,6 +16,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=None, help="positions per cache page (default: the engine's)")
+    ap.add_argument("--max-requests", type=int, default=4, help="state slots: the most requests that are live at any time")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
@@ -26,7 +27,7 @@ def main(argv=None) -> int:
     out.mkdir(parents=True, exist_ok=True)
     engine = Engine.from_folder(args.model, dtype=args.dtype, device=args.device,
                                 page_size=args.page_size or DEFAULT_PAGE_SIZE,
-                                max_tokens=args.max_tokens, max_requests=8)
+                                max_tokens=args.max_tokens, max_requests=args.max_requests)
     live = set()
     for line in sys.stdin:
         line = line.strip()

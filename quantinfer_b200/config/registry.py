@@ -73,6 +73,9 @@ def _register_builtin() -> None:
     from .bebuvik import ARCHITECTURE as BEBUVIK, BebuvikConfig
 
     register_architecture(BEBUVIK, BebuvikConfig)
+    from .kiruvik import ARCHITECTURE as KIRUVIK, KiruvikConfig
+
+    register_architecture(KIRUVIK, KiruvikConfig)
 
 
 _register_builtin()

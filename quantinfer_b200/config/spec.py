@@ -22,7 +22,9 @@ from typing import Optional
 @dataclass(frozen=True)
 class NormSpec:
     """`kind` "rmsnorm": gain per coordinate, tensor `prefix + "weight"`. "rmsnorm_scalar": one gain for all
-    coordinates, the tensor named `prefix` itself, of shape []."""
+    coordinates, the tensor named `prefix` itself, of shape []. "dyt": dynamic tanh, tanh(alpha x) w + b with no
+    statistic of the row (eps unused): w is the tensor named `prefix` itself, b `prefix + ".b"`, alpha
+    `prefix + ".alpha"` of shape []."""
 
     size: int
     eps: float
@@ -70,6 +72,7 @@ class FeedForwardSpec:
     activation: str = "silu"
     prefix: str = ""
     kind: str = "gated_mlp"
+    names: Optional[tuple] = None     # (gate, up, down) tensor names after the prefix; None: the *_proj.weight names
 
 
 @dataclass(frozen=True)
@@ -169,6 +172,104 @@ class BigramEmbeddingSpec:
 
 
 @dataclass(frozen=True)
+class GatedAttentionSpec:
+    """Causal grouped-query attention whose projections have biases (q, k, v and the output; tensors `q`, `k`,
+    `v`, `o`, each with `.b`), whose values may have another size than its keys, and whose concatenated heads are
+    multiplied by sigmoid(W_g x) (`g`, when `out_gate`) before the output projection. `chunk`: a query sees only
+    the keys of its own chunk of that many positions, counted from the sequence's start; `window`: the last n keys;
+    both None: every earlier key. `position`: a :class:`RotarySpec` over the first coordinates of each head, or None."""
+
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    position: Optional[RotarySpec]
+    scale: float
+    chunk: Optional[int] = None
+    window: Optional[int] = None
+    bias: bool = True
+    out_gate: bool = True
+    prefix: str = ""
+    kind: str = "gated_attention"
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """A selective state-space mixer with one decay a head: `heads` heads of `head_dim` channels, a state of
+    `state` x `head_dim` numbers a head, B and C shared by the heads of a group (`groups`), an input convolution of
+    `conv_taps` taps with bias and silu over x | B | C, the gate silu(z) before an RMS norm in `norm_groups` equal
+    parts. Tensors after the prefix: `in` [2 inner + 2 groups state + heads, hidden], `conv` [channels, taps],
+    `conv.b`, `dt_bias`, `A_log`, `D` [heads], `norm` [inner], `o` [hidden, inner]."""
+
+    hidden_size: int
+    heads: int
+    head_dim: int
+    state: int
+    groups: int
+    conv_taps: int
+    norm_groups: int
+    norm_eps: float
+    prefix: str = ""
+    kind: str = "mamba2"
+
+
+@dataclass(frozen=True)
+class ClampedGLUSpec:
+    """Feed-forward down(g sigmoid(alpha g) (u + 1)) with g = min(gate(x), limit), u = clamp(up(x), -limit, limit);
+    no biases; tensors `gate`, `up`, `down` after the prefix."""
+
+    hidden_size: int
+    intermediate_size: int
+    limit: float
+    alpha: float = 1.702
+    prefix: str = ""
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Mixture of `experts` small feed-forwards of the :class:`ClampedGLUSpec` form (`e<k>.gate` and so on), of which
+    a token uses `top`: scores = softmax of the router's logits over all experts (32-bit); the choice is by score +
+    `correction`, the weights are the chosen scores over their sum (+ 1e-20) times `router_scale`. `shared`
+    (optional) runs for every token and is added."""
+
+    hidden_size: int
+    experts: int
+    top: int
+    router_scale: float
+    expert: ClampedGLUSpec            # its prefix is the feed-forward's; expert k's tensors follow `e<k>.`
+    shared: Optional[ClampedGLUSpec] = None
+    prefix: str = ""
+    kind: str = "moe"
+
+
+@dataclass(frozen=True)
+class SandwichLayerSpec:
+    """One block with a norm before AND after each sublayer and a multiplier on what joins the stream:
+    x += m * post1(mixer(pre1(x))); x += m * post2(ffn(pre2(x))). `ffn` (with its norms) may be None."""
+
+    mixer_norm: NormSpec
+    mixer_post_norm: NormSpec
+    mixer: object
+    ffn_norm: Optional[NormSpec]
+    ffn_post_norm: Optional[NormSpec]
+    ffn: object
+    residual_mult: float = 1.0
+    kind: str = "sandwich"
+
+
+@dataclass(frozen=True)
+class ReentrySpec:
+    """What a pass of a looped stretch of layers begins with: x <- W [x ; x0], x0 the embedding's output,
+    W the tensor `weight_name` [hidden, 2 hidden]."""
+
+    hidden_size: int
+    weight_name: str
+    kind: str = "concat_proj"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: x += mixer(norm(x)); x += ffn(norm(x)) for kind `prenorm`."""
 
@@ -190,6 +291,7 @@ class LayerCall:
     layer: int
     cache: int
     writes_cache: bool = True
+    reenter: bool = False      # the model's re-entry part (ModelSpec.reentry) runs right before this call
 
 
 @dataclass(frozen=True)
@@ -225,6 +327,7 @@ class ModelSpec:
     head: HeadSpec
     eos_token_id: Optional[int] = None
     extra: dict = field(default_factory=dict, compare=False)
+    reentry: Optional[ReentrySpec] = None
 
     def cache_entries(self) -> int:
         return 1 + max(call.cache for call in self.order) if self.order else 0
@@ -240,6 +343,8 @@ class ModelSpec:
                 raise ConfigError(f"run order entry {i} names layer {call.layer}, the model has {len(self.layers)}")
             if call.cache < 0:
                 raise ConfigError(f"run order entry {i} has a negative cache entry")
+            if call.reenter and self.reentry is None:
+                raise ConfigError(f"run order entry {i} re-enters, but the model has no re-entry part")
             if call.writes_cache:
                 if call.cache in written:
                     raise ConfigError(f"run order entry {i}: cache entry {call.cache} already has a writer")

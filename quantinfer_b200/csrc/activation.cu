@@ -152,3 +152,35 @@ extern "C" int qi_softcap(float* x, long long n, float cap, cudaStream_t stream)
     qi::launch(softcap_kernel, dim3(blocks_for((size_t)n)), dim3(256), 0, stream, x, (size_t)n, cap, 1.0f / cap);
     return qi::check_launch("softcap");
 }
+
+// ---- the clamped gated unit of small expert feed-forwards ------------------------------------------------
+//   g = min(gate, limit) ; u = clamp(up, -limit, limit) ; out = g * sigmoid(alpha * g) * (u + 1)
+// gate and up side by side or interleaved in rows of 2 I, as for act_mul; 32-bit arithmetic.
+namespace {
+
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gate_up, T* __restrict__ out, size_t n_rows, int inter, int interleaved,
+                                   float limit, float alpha) {
+    qi::pdl_wait();
+    const size_t total = n_rows * inter;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / inter, i = idx % inter;
+        const T* row = gate_up + t * 2 * inter;
+        const float g = fminf(qi::to_f32<T>(interleaved ? row[2 * i] : row[i]), limit);
+        const float u = fminf(fmaxf(qi::to_f32<T>(interleaved ? row[2 * i + 1] : row[inter + i]), -limit), limit);
+        out[idx] = qi::from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+}  // namespace
+
+extern "C" int qi_glu_clamped(const void* gate_up, void* out, int dtype, long long n_rows, int inter, int interleaved, float limit,
+                              float alpha, cudaStream_t stream) {
+    QI_REQUIRE(n_rows >= 0 && inter > 0, "glu_clamped: bad sizes");
+    if (n_rows == 0) return 0;
+    QI_DISPATCH_DTYPE(dtype, T, {
+        qi::launch(glu_clamped_kernel<T>, dim3(blocks_for((size_t)n_rows * inter)), dim3(256), 0, stream, (const T*)gate_up, (T*)out,
+                   (size_t)n_rows, inter, interleaved, limit, alpha);
+    });
+    return qi::check_launch("glu_clamped");
+}

@@ -6,7 +6,12 @@
 // (kv head h / (nq / nkv): consecutive query heads share a kv head):
 //     score_j = (sum_i q_i k_{j,i}) * scale          for lo <= j <= p
 //     out     = sum_j softmax(score)_j * v_j
-// with lo = 0, or p - window + 1 for a windowed layer. Scores, the maximum,
+// with lo = 0, or p - window + 1 for a windowed layer, or the start of p's chunk
+// (floor(p / chunk) * chunk, chunks counted from the sequence's first position)
+// for a chunked layer; both bounds may hold at once. Values may have another
+// size `dv` than queries and keys, and the result may be multiplied, element by
+// element, by the sigmoid of a gate row (an output gate computed from the
+// mixer's input). Scores, the maximum,
 // the exponentials and the weighted sum are 32-bit. This is the reference's
 // loop (crates/quantinfer-runtime/src/attention.rs:105-135; group :83,
 // scale :84, causal bound :106,111) with the softmax evaluated online, one
@@ -30,11 +35,12 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
                          const T* __restrict__ v_pages, const int* __restrict__ block_table,
                          int max_blocks, int page_size, int num_pages,
                          const int* __restrict__ positions, const int* __restrict__ token_req,
-                         int nq, int nkv, int d, float scale, int window, int* __restrict__ status) {
+                         int nq, int nkv, int d, int dv, float scale, int window, int chunk,
+                         const T* __restrict__ gate, long long ldg, int* __restrict__ status) {
     extern __shared__ float smem[];
     float* q_s = smem;                          // [d]
-    float* part_acc = smem + d;                 // [kWarps][d]
-    float* part_m = part_acc + kWarps * d;      // [kWarps]
+    float* part_acc = smem + d;                 // [kWarps][dv]
+    float* part_m = part_acc + kWarps * dv;     // [kWarps]
     float* part_l = part_m + kWarps;            // [kWarps]
 
     qi::pdl_enter();
@@ -44,7 +50,8 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
     const int pos = positions[t];
     const int r = token_req[t];
     const int* table = block_table + (size_t)r * max_blocks;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
 
     const T* qrow = q + ((size_t)t * nq + h) * d;
     for (int i = threadIdx.x; i < d; i += blockDim.x) q_s[i] = qi::to_f32<T>(qrow[i]);
@@ -85,11 +92,11 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
             const int key = base + jj;
             const int page = table[key / page_size];
             if (page < 0 || page >= num_pages) continue;
-            const T* vrow = v_pages + (((size_t)page * nkv + hk) * page_size + (key % page_size)) * (size_t)d;
+            const T* vrow = v_pages + (((size_t)page * nkv + hk) * page_size + (key % page_size)) * (size_t)dv;
 #pragma unroll
             for (int i = 0; i < kAccPerLane; ++i) {
                 const int idx = lane + 32 * i;
-                if (idx < d) acc[i] = fmaf(pj, qi::to_f32<T>(vrow[idx]), acc[i]);
+                if (idx < dv) acc[i] = fmaf(pj, qi::to_f32<T>(vrow[idx]), acc[i]);
             }
         }
         m = m_new;
@@ -103,7 +110,7 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
 #pragma unroll
     for (int i = 0; i < kAccPerLane; ++i) {
         const int idx = lane + 32 * i;
-        if (idx < d) part_acc[warp * d + idx] = acc[i];
+        if (idx < dv) part_acc[warp * dv + idx] = acc[i];
     }
     __syncthreads();
 
@@ -115,39 +122,56 @@ attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* 
         wscale[w] = (part_m[w] == -INFINITY) ? 0.f : expf(part_m[w] - gm);
         gl += part_l[w] * wscale[w];
     }
-    T* orow = out + ((size_t)t * nq + h) * d;
-    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    T* orow = out + ((size_t)t * nq + h) * dv;
+    const T* grow = gate ? gate + (size_t)t * ldg + (size_t)h * dv : nullptr;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
         float o = 0.f;
-        for (int w = 0; w < kWarps; ++w) o += part_acc[w * d + i] * wscale[w];
-        orow[i] = qi::from_f32<T>(gl > 0.f ? o / gl : 0.f);
+        for (int w = 0; w < kWarps; ++w) o += part_acc[w * dv + i] * wscale[w];
+        o = gl > 0.f ? o / gl : 0.f;
+        if (grow) o = o / (1.0f + expf(-qi::to_f32<T>(grow[i])));
+        orow[i] = qi::from_f32<T>(o);
     }
 }
 
 }  // namespace
 
-extern "C" int qi_attention_generic(const void* q, void* out, int dtype, const void* k_pages,
-                                    const void* v_pages, const int* block_table, int max_blocks,
-                                    int page_size, int num_pages, const int* positions,
-                                    const int* token_req, int n_tokens, int nq, int nkv, int d,
-                                    float scale, int window, int* status, cudaStream_t stream) {
-    QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0, "attention: bad sizes");
+// q [n, nq d]; out [n, nq dv]; k_pages [pages, nkv, page_size, d]; v_pages [pages, nkv, page_size, dv];
+// window 0: no window; chunk 0: no chunks; gate (may be null): row t, head h, element i at gate[t * ldg + h * dv + i].
+extern "C" int qi_attention_generic_ex(const void* q, void* out, int dtype, const void* k_pages,
+                                       const void* v_pages, const int* block_table, int max_blocks,
+                                       int page_size, int num_pages, const int* positions,
+                                       const int* token_req, int n_tokens, int nq, int nkv, int d, int dv,
+                                       float scale, int window, int chunk, const void* gate, long long ldg,
+                                       int* status, cudaStream_t stream) {
+    QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "attention: bad sizes");
     QI_REQUIRE(nq % nkv == 0, "attention: %d query heads are not a multiple of %d kv heads", nq, nkv);
-    QI_REQUIRE(d <= kMaxD, "attention: head_dim %d is above the limit %d of this kernel", d, kMaxD);
+    QI_REQUIRE(d <= kMaxD && dv <= kMaxD, "attention: head sizes %d / %d are above the limit %d of this kernel", d, dv, kMaxD);
     QI_REQUIRE(page_size > 0 && max_blocks > 0 && num_pages > 0, "attention: bad page geometry");
-    QI_REQUIRE(window >= 0, "attention: window must be >= 0 (0 = all keys)");
+    QI_REQUIRE(window >= 0 && chunk >= 0, "attention: window and chunk must be >= 0 (0 = none)");
+    QI_REQUIRE(!gate || ldg >= (long long)nq * dv, "attention: the gate's rows are too short");
     QI_REQUIRE(n_tokens <= 65535 * 32768 && nq <= 65535, "attention: grid too large");
     if (n_tokens == 0) return 0;
-    const size_t smem = sizeof(float) * ((size_t)d + kWarps * d + 2 * kWarps);
+    const size_t smem = sizeof(float) * ((size_t)d + kWarps * dv + 2 * kWarps);
     // grid.y is limited to 65535: launch in slabs of tokens.
     for (int t0 = 0; t0 < n_tokens; t0 += 65535) {
         const int nt = n_tokens - t0 < 65535 ? n_tokens - t0 : 65535;
         dim3 grid(nq, nt);
         QI_DISPATCH_DTYPE(dtype, T, {
             qi::launch(attention_generic_kernel<T>, grid, dim3(kWarps * 32), smem, stream,
-                (const T*)q + (size_t)t0 * nq * d, (T*)out + (size_t)t0 * nq * d, (const T*)k_pages,
+                (const T*)q + (size_t)t0 * nq * d, (T*)out + (size_t)t0 * nq * dv, (const T*)k_pages,
                 (const T*)v_pages, block_table, max_blocks, page_size, num_pages, positions + t0,
-                token_req + t0, nq, nkv, d, scale, window, status);
+                token_req + t0, nq, nkv, d, dv, scale, window, chunk,
+                gate ? (const T*)gate + (size_t)t0 * ldg : (const T*)nullptr, ldg, status);
         });
     }
     return qi::check_launch("attention_generic");
+}
+
+extern "C" int qi_attention_generic(const void* q, void* out, int dtype, const void* k_pages,
+                                    const void* v_pages, const int* block_table, int max_blocks,
+                                    int page_size, int num_pages, const int* positions,
+                                    const int* token_req, int n_tokens, int nq, int nkv, int d,
+                                    float scale, int window, int* status, cudaStream_t stream) {
+    return qi_attention_generic_ex(q, out, dtype, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, positions,
+                                   token_req, n_tokens, nq, nkv, d, d, scale, window, 0, nullptr, 0, status, stream);
 }

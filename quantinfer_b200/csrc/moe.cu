@@ -1,0 +1,278 @@
+// Mixture of experts: routing, grouping of the tokens by expert, the experts' products as one grouped
+// launch, and the weighted sum.
+//
+//   moe_route     per token: s = softmax(router logits) over all experts (32-bit); the `top` experts with the
+//                 largest s + correction are chosen (ties: the lower index); their weights are their s divided
+//                 by the sum of the chosen s (+ 1e-20) and multiplied by `scale`.
+//   moe_group     the (token, choice) pairs sorted by expert: offsets per expert, the pairs' order, each pair's
+//                 place in that order, and a list of row tiles (expert, first row, rows) of at most `tile` rows
+//                 that no expert shares with another. One block; everything stays on the device, so a step
+//                 never waits for the host to learn how many tokens an expert got.
+//   moe_gemm      y[i] = W[expert of row i] . x[source of row i] over the sorted rows i, 32-bit products and
+//                 sums with k ascending (the 32-bit path, and any type the tensor-core kernel does not take);
+//                 a row's result does not depend on which other rows its expert got.
+//   moe_combine   out[t] = sum_k weight[t, k] * y[place of (t, k)] (+ shared[t]), k ascending, 32-bit.
+#include "common.cuh"
+
+#include <math.h>
+
+namespace {
+
+constexpr int kMaxPerLane = 32;   // experts a lane holds: up to 1,024 experts
+
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ correction, int* __restrict__ ids,
+                 float* __restrict__ weights, int n, int E, int top, float scale) {
+    qi::pdl_wait();
+    const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= n) return;
+    const float* z = logits + (size_t)t * E;
+    float s[kMaxPerLane], c[kMaxPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        s[i] = e < E ? z[e] : -INFINITY;
+        m = fmaxf(m, s[i]);
+    }
+    m = qi::warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        s[i] = e < E ? expf(s[i] - m) : 0.f;
+        sum += s[i];
+    }
+    sum = qi::warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < kMaxPerLane; ++i) {
+        const int e = lane + 32 * i;
+        s[i] = s[i] / sum;
+        c[i] = e < E ? s[i] + (correction ? correction[e] : 0.f) : -INFINITY;
+    }
+    float chosen_sum = 0.f;
+    float my_w = 0.f;      // lane k keeps the k-th choice's score
+    int my_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i) {
+            const int e = lane + 32 * i;
+            if (c[i] > best) { best = c[i]; best_e = e; }      // e ascends with i: the lower index wins a tie
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+        }
+        float sc = 0.f;
+#pragma unroll
+        for (int i = 0; i < kMaxPerLane; ++i)
+            if (lane + 32 * i == best_e) { sc = s[i]; c[i] = -INFINITY; }
+        sc = qi::warp_sum(sc);
+        chosen_sum += sc;
+        if (k == lane) { my_w = sc; my_id = best_e; }      // lane k keeps choice k (top <= 32)
+    }
+    const float inv = scale / (chosen_sum + 1e-20f);
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = my_id;
+        weights[(size_t)t * top + lane] = my_w * inv;
+    }
+}
+
+// One block. smem: counts[E], offsets[E + 1], tile_base[E + 1].
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int tile, int max_tiles, int* __restrict__ offsets,
+                 int* __restrict__ order, int* __restrict__ place, int* __restrict__ tiles) {
+    extern __shared__ int sm[];
+    int* counts = sm;
+    int* offs = sm + E;
+    int* tbase = offs + E + 1;
+    qi::pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int a = 0, b = 0;
+        for (int e = 0; e < E; ++e) {
+            offs[e] = a; tbase[e] = b;
+            a += counts[e];
+            b += (counts[e] + tile - 1) / tile;
+        }
+        offs[E] = a; tbase[E] = b;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = offs[e];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int cnt = counts[e];
+        int k = tbase[e];
+        for (int r0 = 0; r0 < cnt; r0 += tile, ++k) {
+            if (k < max_tiles) { tiles[3 * k] = e; tiles[3 * k + 1] = offs[e] + r0; tiles[3 * k + 2] = min(tile, cnt - r0); }
+        }
+    }
+    for (int k = tbase[E] + threadIdx.x; k < max_tiles; k += blockDim.x) { tiles[3 * k] = -1; tiles[3 * k + 1] = 0; tiles[3 * k + 2] = 0; }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = offs[e];     // cursors
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+        const int e = ids[i];
+        if (e < 0 || e >= E) continue;
+        const int pos = atomicAdd(&counts[e], 1);
+        order[pos] = i;
+        place[i] = pos;
+    }
+}
+
+constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;
+
+// Rows are the sorted (token, choice) pairs; a tile's rows belong to one expert. Source row of sorted row i:
+// order[i] / top when `gather` (the experts read the tokens' rows), else i (they read rows already in sorted order).
+template <typename TX, typename TW, typename TY>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, const int* __restrict__ tiles,
+                const int* __restrict__ order, int top, int gather, int N, int K, long long ldx, long long ldy) {
+    __shared__ float xs[BK][BM + 4];
+    __shared__ float ws[BK][BN + 4];
+    __shared__ int src_row[BM];
+    qi::pdl_wait();
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    if (expert < 0) return;
+    const TW* we = w + (size_t)expert * N * K;
+    const int tid = threadIdx.x;
+    const int tx = tid % 16, ty = tid / 16;  // tx over N (16 x TN = 64), ty over M (16 x TM = 32)
+    const int n0 = blockIdx.x * BN;
+    if (tid < BM) src_row[tid] = tid < rows ? (gather ? order[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+
+    const int lrow = tid / 4;        // 0..63
+    const int lk = (tid % 4) * 4;    // 0,4,8,12
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            float a = 0.f, b = 0.f;
+            if (k < K) {
+                if (lrow < BM && src_row[lrow] >= 0) a = qi::to_f32<TX>(x[(size_t)src_row[lrow] * ldx + k]);
+                if (n0 + lrow < N) b = qi::to_f32<TW>(we[(size_t)(n0 + lrow) * K + k]);
+            }
+            if (lrow < BM) xs[lk + i][lrow] = a;
+            ws[lk + i][lrow] = b;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = xs[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) b[j] = ws[k][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = ty * TM + i;
+        if (m >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n < N) y[(size_t)(row0 + m) * ldy + n] = qi::from_f32<TY>(acc[i][j]);
+        }
+    }
+}
+
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                   const TY* __restrict__ shared, TO* __restrict__ out, int n, int top, int width) {
+    qi::pdl_wait();
+    const size_t total = (size_t)n * width;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / width;
+        const int c = (int)(idx % width);
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k)
+            acc = fmaf(weights[t * top + k], qi::to_f32<TY>(y[(size_t)place[t * top + k] * width + c]), acc);
+        if (shared) acc += qi::to_f32<TY>(shared[idx]);
+        out[idx] = qi::from_f32<TO>(acc);
+    }
+}
+
+}  // namespace
+
+extern "C" int qi_moe_tile_rows() { return BM; }
+
+// logits float32 [n, E]; correction float32 [E] or null; ids int32 [n, top]; weights float32 [n, top].
+extern "C" int qi_moe_route(const float* logits, const float* correction, int* ids, float* weights, int n, int E, int top,
+                            float scale, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes n=%d experts=%d top=%d", n, E, top);
+    QI_REQUIRE(E <= 32 * kMaxPerLane, "moe_route: %d experts are above this kernel's %d", E, 32 * kMaxPerLane);
+    QI_REQUIRE(top <= 32, "moe_route: %d choices a token are above this kernel's 32", top);
+    if (n == 0) return 0;
+    qi::launch(moe_route_kernel, dim3((n + 3) / 4), dim3(128), 0, stream, logits, correction, ids, weights, n, E, top, scale);
+    return qi::check_launch("moe_route");
+}
+
+// ids int32 [n_pairs]; offsets int32 [E + 1]; order, place int32 [n_pairs]; tiles int32 [max_tiles, 3] with
+// max_tiles >= n_pairs / tile + E.
+extern "C" int qi_moe_group(const int* ids, int n_pairs, int E, int tile, int max_tiles, int* offsets, int* order, int* place,
+                            int* tiles, cudaStream_t stream) {
+    QI_REQUIRE(n_pairs >= 0 && E > 0 && tile > 0, "moe_group: bad sizes");
+    QI_REQUIRE(max_tiles >= n_pairs / tile + E || max_tiles >= n_pairs, "moe_group: the tile list is too short");
+    QI_REQUIRE(E <= 4096, "moe_group: too many experts");
+    qi::launch(moe_group_kernel, dim3(1), dim3(1024), sizeof(int) * (3 * (size_t)E + 2), stream, ids, n_pairs, E, tile, max_tiles,
+               offsets, order, place, tiles);
+    return qi::check_launch("moe_group");
+}
+
+// x rows of K (ldx apart); w [E, N, K]; y [n_rows, N] (ldy apart); tiles as moe_group wrote them with tile = qi_moe_tile_rows().
+extern "C" int qi_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, const int* tiles,
+                           int max_tiles, const int* order, int top, int gather, int N, int K, long long ldx, long long ldy,
+                           cudaStream_t stream) {
+    QI_REQUIRE(max_tiles >= 0 && N > 0 && K > 0 && top > 0, "moe_gemm: bad sizes");
+    QI_REQUIRE(ldx >= K && ldy >= N, "moe_gemm: a leading dimension is smaller than its row");
+    QI_REQUIRE(max_tiles <= 65535, "moe_gemm: %d row tiles are too many for one launch", max_tiles);
+    if (max_tiles == 0) return 0;
+    const dim3 grid((N + BN - 1) / BN, max_tiles), block(256);
+    QI_DISPATCH_DTYPE(x_dtype, TX, {
+        QI_DISPATCH_DTYPE(w_dtype, TW, {
+            QI_DISPATCH_DTYPE(y_dtype, TY, {
+                qi::launch(moe_gemm_kernel<TX, TW, TY>, grid, block, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, tiles, order, top,
+                           gather, N, K, ldx, ldy);
+            });
+        });
+    });
+    return qi::check_launch("moe_gemm");
+}
+
+// y [n * top, width] in y_dtype (sorted rows); place int32 [n, top]; weights float32 [n, top]; shared [n, width] in y_dtype or null.
+extern "C" int qi_moe_combine(const void* y, int y_dtype, const int* place, const float* weights, const void* shared, void* out,
+                              int out_dtype, int n, int top, int width, cudaStream_t stream) {
+    QI_REQUIRE(n >= 0 && top > 0 && width > 0, "moe_combine: bad sizes");
+    if (n == 0) return 0;
+    size_t blocks = ((size_t)n * width + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    QI_DISPATCH_DTYPE(y_dtype, TY, {
+        QI_DISPATCH_DTYPE(out_dtype, TO, {
+            qi::launch(moe_combine_kernel<TY, TO>, dim3((unsigned)blocks), dim3(256), 0, stream, (const TY*)y, place, weights,
+                       (const TY*)shared, (TO*)out, n, top, width);
+        });
+    });
+    return qi::check_launch("moe_combine");
+}

@@ -290,3 +290,88 @@ extern "C" int qi_qk_norm_rope_kv(const void* qkv, int qkv_splits, void* q_out, 
     });
     return qi::check_launch("qk_norm_rope_kv");
 }
+
+// ---- biases, rotation by angles computed where they are used, and the cache write ----------------------
+//
+// For designs whose projections have biases, whose values may have another size than their keys, and
+// which set no limit on positions (so there is no table): a row of `proj` holds q (nq heads of d), k (nkv
+// heads of d) and v (nkv heads of dv) side by side, possibly followed by more columns (`ld` elements a
+// row). The bias (32-bit, q | k | v, may be null) is added, the first `rot` coordinates of every q and k
+// head turn by angle = position * inv_freq[pair] (32-bit product, sincosf), pairs (i, i + rot / 2) or, when
+// `interleaved`, (2i, 2i + 1); q goes to q_out [n, nq d], k and v into the request's pages
+// (k_pages [pages, nkv, page_size, d], v_pages [pages, nkv, page_size, dv]; null: nothing is written).
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_rope_kv_kernel(const T* __restrict__ proj, long long ld, const float* __restrict__ bias, T* __restrict__ q_out,
+                    const float* __restrict__ inv_freq, int rot, int interleaved, const int* __restrict__ positions,
+                    const int* __restrict__ token_req, const int* __restrict__ block_table, int max_blocks, int page_size,
+                    int num_pages, T* __restrict__ k_pages, T* __restrict__ v_pages, int nq, int nkv, int d, int dv,
+                    int* __restrict__ status) {
+    qi::pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    if (pos < 0) {
+        if (threadIdx.x == 0 && status) atomicOr(status, qi::kStatusBadRange);
+        return;
+    }
+    const T* row = proj + (size_t)t * ld;
+    const int qk = (nq + nkv) * d, total = qk + nkv * dv;
+    T* krow = nullptr;
+    T* vrow = nullptr;
+    if (k_pages) {
+        const int page = block_table[(size_t)token_req[t] * max_blocks + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0 && status) atomicOr(status, qi::kStatusBadPage);
+        } else {
+            krow = k_pages + ((size_t)page * nkv * page_size + (pos % page_size)) * (size_t)d;
+            vrow = v_pages + ((size_t)page * nkv * page_size + (pos % page_size)) * (size_t)dv;
+        }
+    }
+    const int half = rot / 2;
+    for (int e = threadIdx.x; e < total; e += blockDim.x) {
+        if (e >= qk) {   // a value: bias only
+            const int hv = (e - qk) / dv, i = (e - qk) % dv;
+            const float v = qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f);
+            if (vrow) vrow[(size_t)hv * page_size * dv + i] = qi::from_f32<T>(v);
+            continue;
+        }
+        const int head = e / d, i = e % d;
+        float x = qi::to_f32<T>(row[e]) + (bias ? bias[e] : 0.f);
+        if (i < rot) {
+            int pair, other;
+            bool first;
+            if (interleaved) { pair = i >> 1; first = !(i & 1); other = first ? e + 1 : e - 1; }
+            else { first = i < half; pair = first ? i : i - half; other = first ? e + half : e - half; }
+            const float o = qi::to_f32<T>(row[other]) + (bias ? bias[other] : 0.f);
+            float sn, cs;
+            sincosf((float)pos * inv_freq[pair], &sn, &cs);
+            x = first ? x * cs - o * sn : x * cs + o * sn;
+        }
+        if (head < nq) q_out[(size_t)t * nq * d + e] = qi::from_f32<T>(x);
+        else if (krow) krow[(size_t)(head - nq) * page_size * d + i] = qi::from_f32<T>(x);
+    }
+}
+
+}  // namespace
+
+extern "C" int qi_bias_rope_kv(const void* proj, long long ld, const float* bias, void* q_out, int dtype,
+                               const float* inv_freq, int rot, int interleaved, const int* positions,
+                               const int* token_req, const int* block_table, int max_blocks, int page_size,
+                               int num_pages, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv, int d,
+                               int dv, int* status, cudaStream_t stream) {
+    QI_REQUIRE(n_tokens >= 0 && nq > 0 && nkv > 0 && d > 0 && dv > 0, "bias_rope_kv: bad sizes");
+    QI_REQUIRE(rot >= 0 && rot % 2 == 0 && rot <= d, "bias_rope_kv: %d rotated coordinates do not fit a head of %d", rot, d);
+    QI_REQUIRE(rot == 0 || inv_freq, "bias_rope_kv: a rotation needs its inverse frequencies");
+    QI_REQUIRE(ld >= (long long)(nq + nkv) * d + (long long)nkv * dv, "bias_rope_kv: the rows are too short");
+    QI_REQUIRE((k_pages == nullptr) == (v_pages == nullptr), "bias_rope_kv: key and value pages come together");
+    QI_REQUIRE(!k_pages || (block_table && max_blocks > 0 && page_size > 0 && num_pages > 0), "bias_rope_kv: bad page geometry");
+    if (n_tokens == 0) return 0;
+    QI_DISPATCH_DTYPE(dtype, T, {
+        qi::launch(bias_rope_kv_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, bias, (T*)q_out, inv_freq, rot,
+                   interleaved, positions, token_req, block_table, max_blocks, page_size, num_pages, (T*)k_pages, (T*)v_pages,
+                   nq, nkv, d, dv, status);
+    });
+    return qi::check_launch("bias_rope_kv");
+}

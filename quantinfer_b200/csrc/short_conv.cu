@@ -8,7 +8,10 @@
 // launch (a layer whose sublayers each have their own filter over one normalised stream), and the
 // input can be written once more in the output type (for a consumer that reads it unfiltered).
 //
-// Inputs and state are 32-bit; sums are 32-bit; outputs in the activation type. Weights are laid out
+// A bias per channel may be added and silu applied to the sum (`act` 1), as the input convolution of a
+// recurrent layer wants; the input may then be a block of columns inside wider rows (`ldh` elements a row)
+// in the activation type.
+// The state and all sums are 32-bit; inputs 32-bit or the activation type; outputs in the activation type. Weights are laid out
 // [filter][tap][channel] so that a warp's loads are contiguous.
 //
 // One thread per (token, channel). A token that stands at least taps - 1 places into its entry reads
@@ -22,9 +25,15 @@ namespace {
 
 constexpr int kMaxTaps = 16;
 
-template <typename TO>
+__device__ __forceinline__ float conv_finish(float a, const float* bias, int c, int act) {
+    if (bias) a += bias[c];
+    return act == 1 ? a / (1.0f + expf(-a)) : a;
+}
+
+template <typename TI, typename TO>
 __global__ void __launch_bounds__(256)
-short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, float* __restrict__ state,
+short_conv_kernel(const TI* __restrict__ h, long long ldh, const float* __restrict__ bias, int act,
+                  const float* __restrict__ w, float* __restrict__ state,
                   TO* __restrict__ out0, TO* __restrict__ out1, TO* __restrict__ copy,
                   const int* __restrict__ token_req, const int* __restrict__ q_start,
                   const int* __restrict__ start_pos, const int* __restrict__ slot_ids, int n_tokens, int C,
@@ -36,19 +45,19 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
     const int e = token_req[t];
     const int first = q_start[e];
     const int i = t - first;
-    const float x = h[idx];
+    const float x = qi::to_f32<TI>(h[(size_t)t * ldh + c]);
     if (copy) copy[idx] = qi::from_f32<TO>(x);
     const int back = taps - 1;
     const float* w1 = w + (size_t)taps * C;
     if (i >= back) {
         float a0 = residual ? x : 0.f, a1 = a0;
         for (int j = 0; j < taps; ++j) {
-            const float v = h[(size_t)(t - back + j) * C + c];
+            const float v = qi::to_f32<TI>(h[(size_t)(t - back + j) * ldh + c]);
             a0 = fmaf(w[(size_t)j * C + c], v, a0);
             if (n_filters > 1) a1 = fmaf(w1[(size_t)j * C + c], v, a1);
         }
-        out0[idx] = qi::from_f32<TO>(a0);
-        if (n_filters > 1) out1[idx] = qi::from_f32<TO>(a1);
+        out0[idx] = qi::from_f32<TO>(conv_finish(a0, bias, c, act));
+        if (n_filters > 1) out1[idx] = qi::from_f32<TO>(conv_finish(a1, bias ? bias + C : nullptr, c, act));
         return;
     }
     if (i != 0) return;
@@ -62,13 +71,13 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
     for (int k = 0; k < back; ++k) old[k] = (p0 - back + k >= 0) ? st[(size_t)k * C] : 0.f;
     const int head = len < back ? len : back;
     for (int ii = 0; ii < head; ++ii) {
-        const float xi = h[(size_t)(first + ii) * C + c];
+        const float xi = qi::to_f32<TI>(h[(size_t)(first + ii) * ldh + c]);
         float a0 = residual ? xi : 0.f, a1 = a0;
         for (int j = 0; j < taps; ++j) {
             const int rel = ii - back + j;      // place in the entry; negative: in the old state
             float v;
             if (rel >= 0) {
-                v = h[(size_t)(first + rel) * C + c];
+                v = qi::to_f32<TI>(h[(size_t)(first + rel) * ldh + c]);
             } else {
                 v = 0.f;
 #pragma unroll
@@ -77,14 +86,14 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
             a0 = fmaf(w[(size_t)j * C + c], v, a0);
             if (n_filters > 1) a1 = fmaf(w1[(size_t)j * C + c], v, a1);
         }
-        out0[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(a0);
-        if (n_filters > 1) out1[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(a1);
+        out0[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(conv_finish(a0, bias, c, act));
+        if (n_filters > 1) out1[(size_t)(first + ii) * C + c] = qi::from_f32<TO>(conv_finish(a1, bias ? bias + C : nullptr, c, act));
     }
     for (int k = 0; k < back; ++k) {
         const int rel = len - back + k;
         float v;
         if (rel >= 0) {
-            v = h[(size_t)(first + rel) * C + c];
+            v = qi::to_f32<TI>(h[(size_t)(first + rel) * ldh + c]);
         } else {
             v = 0.f;
 #pragma unroll
@@ -96,24 +105,30 @@ short_conv_kernel(const float* __restrict__ h, const float* __restrict__ w, floa
 
 }  // namespace
 
-// h float32 [n_tokens, C]; w float32 [n_filters, taps, C]; state float32 [slots, taps - 1, C] with `state_stride`
+// h [n_tokens, C] in `in_dtype` with `ldh` elements from row to row; bias float32 [n_filters, C] or null; act 0: none,
+// 1: silu; w float32 [n_filters, taps, C]; state float32 [slots, taps - 1, C] with `state_stride`
 // floats from slot to slot (at least (taps - 1) * C; may be null when taps == 1); out0, out1 (out1 only with two filters) and copy (may be null) [n_tokens, C] in `out_dtype`.
-extern "C" int qi_short_conv(const float* h, const float* w, float* state, void* out0, void* out1, void* copy,
+extern "C" int qi_short_conv(const void* h, int in_dtype, long long ldh, const float* bias, int act, const float* w, float* state,
+                             void* out0, void* out1, void* copy,
                              int out_dtype, const int* token_req, const int* q_start, const int* start_pos,
                              const int* slot_ids, int n_tokens, int channels, int taps, int n_filters, int residual,
                              long long state_stride, cudaStream_t stream) {
     QI_REQUIRE(taps == 1 || state_stride >= (long long)(taps - 1) * channels, "short_conv: the slots of the state overlap");
-    QI_REQUIRE(n_tokens >= 0 && channels > 0, "short_conv: bad sizes n=%d channels=%d", n_tokens, channels);
+    QI_REQUIRE(n_tokens >= 0 && channels > 0 && ldh >= channels, "short_conv: bad sizes n=%d channels=%d", n_tokens, channels);
     QI_REQUIRE(taps >= 1 && taps <= kMaxTaps, "short_conv: %d taps are outside 1..%d", taps, kMaxTaps);
     QI_REQUIRE(n_filters == 1 || n_filters == 2, "short_conv: one or two filters a launch, got %d", n_filters);
     QI_REQUIRE(taps == 1 || state, "short_conv: a filter of more than one tap needs its state");
     QI_REQUIRE(out0 && (n_filters == 1 || out1), "short_conv: an output is missing");
+    QI_REQUIRE(act == 0 || act == 1, "short_conv: unknown activation code %d", act);
     if (n_tokens == 0) return 0;
     const size_t total = (size_t)n_tokens * channels;
     QI_REQUIRE((total + 255) / 256 <= 0x7fffffffull, "short_conv: grid too large");
-    QI_DISPATCH_DTYPE(out_dtype, TO, {
-        qi::launch(short_conv_kernel<TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, h, w, state, (TO*)out0, (TO*)out1,
-                   (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps, n_filters, residual, state_stride);
+    QI_DISPATCH_DTYPE(in_dtype, TI, {
+        QI_DISPATCH_DTYPE(out_dtype, TO, {
+            qi::launch(short_conv_kernel<TI, TO>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const TI*)h, ldh, bias, act,
+                       w, state, (TO*)out0, (TO*)out1, (TO*)copy, token_req, q_start, start_pos, slot_ids, n_tokens, channels, taps,
+                       n_filters, residual, state_stride);
+        });
     });
     return qi::check_launch("short_conv");
 }

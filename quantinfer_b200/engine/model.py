@@ -22,6 +22,8 @@ def tensor_needs_of_spec(spec: ModelSpec) -> dict:
     """{file name: TensorNeed} of the whole model, in a fixed order; needs no device."""
     needs = {}
     needs.update(part_class("embedding", spec.embedding).needs_of_spec(spec.embedding))
+    if getattr(spec, "reentry", None) is not None:
+        needs.update(part_class("reentry", spec.reentry).needs_of_spec(spec.reentry))
     for layer in spec.layers:
         needs.update(part_class("block", layer).needs_of_spec(layer))
     needs.update(part_class("norm", spec.final_norm).needs_of_spec(spec.final_norm))
@@ -38,9 +40,11 @@ class Model:
         self.blocks = [build_part("block", layer, runtime) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head, runtime)
+        self.reentry = build_part("reentry", spec.reentry, runtime) if getattr(spec, "reentry", None) is not None else None
         if spec.head.tied:
             self.head.tie(self.embedding)
         self.order = spec.order
+        self.tap = None               # a caller's probe: called after every layer call with (call, resid, delta)
         self.native = None            # the C++ driver's description of this model (engine/native.py), once asked for
         self.use_native = True
         # what each cache entry must hold comes from the layer that writes it, widened by those that read it
@@ -72,7 +76,7 @@ class Model:
         self.embedding_view = None     # set by the engine when the embedding keeps state
 
     def _parts(self):
-        return (self.embedding, *self.blocks, self.final_norm, self.head)
+        return (self.embedding, *((self.reentry,) if self.reentry is not None else ()), *self.blocks, self.final_norm, self.head)
 
     def tensor_needs(self) -> dict:
         needs = {}
@@ -110,8 +114,14 @@ class Model:
         else:
             resid = self.embedding(batch.token_ids)
         delta = None
+        # a model whose layers re-enter (a looped stretch mixes the embedding's output back in) keeps that output
+        x0 = resid.clone() if self.reentry is not None else None
         for call, view in zip(self.order, cache_views):
+            if call.reenter:
+                resid, delta = self.reentry.forward(resid, delta, x0), None
             resid, delta = self.blocks[call.layer].forward(resid, delta, batch, view)
+            if self.tap is not None:
+                self.tap(call, resid, delta)
         if batch.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=resid.device)
         normed = self.final_norm(resid, delta, rows=batch.logit_rows)

@@ -80,6 +80,8 @@ class NativeProgram:
         from ..parts.norm import RMSNorm
         from ..parts.position import RopeHalfSplit
 
+        if getattr(model, "reentry", None) is not None:
+            return None          # the driver knows no re-entry between layers
         if type(model.embedding) is not Embedding or type(model.head) is not LMHead or type(model.final_norm) is not RMSNorm:
             return None
         if getattr(model.head, "softcap", None) is not None:

@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 
 def status_names(code: int) -> list:
@@ -304,8 +304,11 @@ def qk_norm_rope_kv(qkv, q_out, q_gain, k_gain, eps, cos, sin, rotary_dim, posit
 
 
 def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_req, nq, nkv, d,
-                      scale: float, window: int, status) -> None:
-    """Causal paged GQA attention, 32-bit arithmetic, any span length and page size."""
+                      scale: float, window: int, status, chunk: int = 0, gate=None) -> None:
+    """Causal paged GQA attention, 32-bit arithmetic, any span length and page size. Values may have another
+    size than keys (v_pages [pages, nkv, page_size, dv], out [n, nq dv]); `chunk` > 0: a query sees only the keys
+    of its own chunk of that many positions (counted from the sequence's start); `gate` [n, >= nq dv] (a view whose
+    rows may lie further apart): the result is multiplied by sigmoid(gate)."""
     _req(q, "q", ndim=2)
     _req(out, "out", q.dtype, 2)
     _req(k_pages, "k_pages", q.dtype, 4)
@@ -314,14 +317,20 @@ def attention_generic(q, out, k_pages, v_pages, block_table, positions, token_re
     _req(positions, "positions", torch.int32, 1)
     _req(token_req, "token_req", torch.int32, 1)
     n = q.shape[0]
-    if q.shape[1] != nq * d or out.shape != q.shape:
-        raise KernelError(f"attention: q {tuple(q.shape)} does not match {nq} heads of {d}")
-    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape != v_pages.shape:
-        raise KernelError(f"attention: pages {tuple(k_pages.shape)} do not match {nkv} kv heads of {d}")
-    _call('attention', "attention_generic", library().qi_attention_generic,
+    dv = v_pages.shape[3]
+    if q.shape[1] != nq * d or tuple(out.shape) != (n, nq * dv):
+        raise KernelError(f"attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not match {nq} heads of {d} / {dv}")
+    if k_pages.shape[1] != nkv or k_pages.shape[3] != d or k_pages.shape[:3] != v_pages.shape[:3]:
+        raise KernelError(f"attention: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not match {nkv} kv heads of {d}")
+    ldg = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
+            raise KernelError("attention: the gate must be [n, nq dv] in q's type with contiguous rows")
+        ldg = gate.stride(0)
+    _call('attention', "attention_generic", library().qi_attention_generic_ex,
           _ptr(q), _ptr(out), _code(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table),
         block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(positions), _ptr(token_req), n,
-        nq, nkv, d, C.c_float(scale), int(window or 0), _ptr(status), _stream())
+        nq, nkv, d, dv, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg), _ptr(status), _stream())
 
 
 def attention_mma_supported(nq: int, nkv: int, d: int) -> bool:
@@ -777,12 +786,16 @@ def embedding_bigram(table, bigram, ids, positions, token_req, q_start, slot_ids
           C.c_longlong(mul_prev), C.c_longlong(mul_cur), C.c_longlong(prev_state.stride(0)), _ptr(status), _stream())
 
 
-def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slot_ids, residual: bool = True) -> None:
-    """outs[k][t] = (h[t] if residual) + sum_j weights[k, j] * h[t - taps + 1 + j] per channel, over each request's
-    own time axis: rows before a step's first token come from `state` (float32 [slots, taps - 1, channels], the
-    request's last inputs; advanced by the launch), zeros before the sequence's start. h float32 [n, channels];
-    weights float32 [filters, taps, channels] with one or two filters; `copy`, if given, receives h in its type."""
-    _req(h, "h", torch.float32, 2)
+def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slot_ids, residual: bool = True,
+               bias=None, act: str | None = None) -> None:
+    """outs[k][t] = f((h[t] if residual) + sum_j weights[k, j] * h[t - taps + 1 + j] (+ bias[k])) per channel, over each
+    request's own time axis: rows before a step's first token come from `state` (float32 [slots, taps - 1, channels],
+    the request's last inputs; advanced by the launch), zeros before the sequence's start. h [n, channels], float32 or
+    the outputs' type; it may be a block of columns of wider rows (a view whose rows lie `h.stride(0)` apart);
+    weights float32 [filters, taps, channels] with one or two filters; bias float32 [filters, channels] or None; f is
+    silu when `act` is "silu", else nothing; `copy`, if given, receives h in its type."""
+    if not isinstance(h, torch.Tensor) or not h.is_cuda or h.dim() != 2 or h.stride(1) != 1 or h.stride(0) < h.shape[1]:
+        raise KernelError("short_conv: h must be a CUDA tensor [n, channels] whose rows are contiguous")
     _req(weights, "weights", torch.float32, 3)
     n, ch = h.shape
     filters, taps = weights.shape[0], weights.shape[1]
@@ -792,6 +805,12 @@ def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slo
         _req(o, "out", outs[0].dtype, 2)
         if tuple(o.shape) != (n, ch):
             raise KernelError(f"short_conv: an output is {tuple(o.shape)}, expected {(n, ch)}")
+    if bias is not None:
+        _req(bias, "bias", torch.float32, 2)
+        if tuple(bias.shape) != (filters, ch):
+            raise KernelError(f"short_conv: bias {tuple(bias.shape)} does not fit {filters} filters of {ch} channels")
+    if act not in (None, "silu"):
+        raise KernelError(f"short_conv: activation {act!r} is not known (silu or None)")
     if taps > 1:
         _req_state(state, "state", torch.float32)
         if tuple(state.shape[1:]) != (taps - 1, ch):
@@ -799,7 +818,8 @@ def short_conv(h, weights, state, outs, copy, token_req, q_start, start_pos, slo
     for t, name in ((token_req, "token_req"), (q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
         _req(t, name, torch.int32)
     _call("other", "short_conv", library().qi_short_conv,
-          _ptr(h), _ptr(weights), _ptr(state if taps > 1 else None), _ptr(outs[0]), _ptr(outs[1] if filters > 1 else None),
+          _ptr(h), _code(h), C.c_longlong(h.stride(0)), _ptr(bias), 1 if act == "silu" else 0,
+          _ptr(weights), _ptr(state if taps > 1 else None), _ptr(outs[0]), _ptr(outs[1] if filters > 1 else None),
           _ptr(copy), _code(outs[0]), _ptr(token_req), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), n, ch, taps, filters,
           int(bool(residual)), C.c_longlong(state.stride(0) if taps > 1 else 0), _stream())
 
@@ -973,3 +993,222 @@ def latent_attention(q, out, cache, sink, block_table, q_start, start_pos, posit
           _ptr(q), _ptr(out), _ptr(cache), _ptr(sink), _ptr(block_table), block_table.shape[1], cache.shape[1], cache.shape[0],
           _ptr(q_start), _ptr(start_pos), start_pos.numel(), n, heads, W, R, C.c_float(scale), int(window or 0), key_ranges,
           _ptr(ws_o), _ptr(ws_ml), _ptr(status), _stream())
+
+
+# --------------------------------------------------------------------------
+# dynamic tanh, biases + direct rotation, state-space recurrence, mixture of experts
+
+
+def dyt(resid, y=None, y_bias=None, post=None, mult: float = 1.0, pre=None, out=None, rows=None, write_resid: bool = True) -> None:
+    """The elementwise work around a sublayer of a model normalised by dynamic tanh, dyt(v) = tanh(alpha v) w + b:
+    resid += mult * dyt_post(y + y_bias) (or resid += y + y_bias without `post`), then out = dyt_pre(resid).
+    resid float32 [n, h]; y [n, h] or None; y_bias float32 [h] or None; post, pre: (w, b, alpha) float32 [h], [h], [1]
+    or None; out [n, h] (or [len(rows), h] when `rows` picks source rows; the stream is then not written)."""
+    _req(resid, "resid", torch.float32, 2)
+    n, h = resid.shape
+    if y is not None:
+        _req(y, "y", ndim=2)
+        if tuple(y.shape) != (n, h):
+            raise KernelError(f"dyt: y {tuple(y.shape)} does not match resid {tuple(resid.shape)}")
+    for trio, name in ((post, "post"), (pre, "pre")):
+        if trio is not None:
+            w, b, alpha = trio
+            _req(w, name + " w", torch.float32, 1)
+            _req(b, name + " b", torch.float32, 1)
+            _req(alpha, name + " alpha", torch.float32)
+            if w.numel() != h or b.numel() != h or alpha.numel() != 1:
+                raise KernelError(f"dyt: the {name}-norm's tensors do not fit rows of {h}")
+    if y_bias is not None:
+        _req(y_bias, "y_bias", torch.float32, 1)
+        if y_bias.numel() != h:
+            raise KernelError("dyt: the bias does not fit the rows")
+    n_out = n
+    if rows is not None:
+        _req(rows, "rows", torch.int32, 1)
+        n_out, write_resid = rows.numel(), False
+    if (pre is None) != (out is None):
+        raise KernelError("dyt: a pre-norm and an output come together")
+    if out is not None:
+        _req(out, "out", ndim=2)
+        if tuple(out.shape) != (n_out, h):
+            raise KernelError(f"dyt: out is {tuple(out.shape)}, expected {(n_out, h)}")
+    pw, pb, pa = post if post is not None else (None, None, None)
+    rw, rb, ra = pre if pre is not None else (None, None, None)
+    _call("norm", "dyt", library().qi_dyt, _ptr(resid), _ptr(y), _code(y) if y is not None else F32, _ptr(y_bias),
+          _ptr(pw), _ptr(pb), _ptr(pa), C.c_float(mult), _ptr(rw), _ptr(rb), _ptr(ra), _ptr(out),
+          _code(out) if out is not None else F32, _ptr(rows), n_out, h, int(bool(write_resid)), _stream())
+
+
+def concat_cast(a, b, out) -> None:
+    """out[t] = [a[t] | b[t]]: two float32 streams [n, h] side by side in out's type [n, 2 h]."""
+    _req(a, "a", torch.float32, 2)
+    _req(b, "b", torch.float32, 2)
+    _req(out, "out", ndim=2)
+    n, h = a.shape
+    if b.shape != a.shape or tuple(out.shape) != (n, 2 * h):
+        raise KernelError("concat_cast: shapes do not agree")
+    _call("other", "concat_cast", library().qi_concat_cast, _ptr(a), _ptr(b), _ptr(out), _code(out), n, h, _stream())
+
+
+def bias_rope_kv(proj, bias, q_out, inv_freq, rot: int, interleaved: bool, positions, token_req, block_table, page_size: int,
+                 k_pages, v_pages, nq: int, nkv: int, d: int, dv: int, status) -> None:
+    """proj [n, >= (nq + nkv) d + nkv dv] holds q | k | v (more columns may follow); bias float32 over those columns or
+    None; the first `rot` coordinates of each q and k head turn by position * inv_freq[pair] (computed here in 32-bit:
+    no table, no limit on positions); q goes to q_out [n, nq d], k and v into the pages (None: nothing is written)."""
+    if not proj.is_cuda or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("bias_rope_kv: proj must be a CUDA tensor with contiguous rows")
+    _req(q_out, "q_out", proj.dtype, 2)
+    n = proj.shape[0]
+    cols = (nq + nkv) * d + nkv * dv
+    if proj.shape[1] < cols or tuple(q_out.shape) != (n, nq * d):
+        raise KernelError(f"bias_rope_kv: proj {tuple(proj.shape)} / q_out {tuple(q_out.shape)} do not match the heads")
+    if bias is not None:
+        _req(bias, "bias", torch.float32, 1)
+        if bias.numel() != cols:
+            raise KernelError("bias_rope_kv: the bias does not fit q | k | v")
+    if rot:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.numel() * 2 != rot:
+            raise KernelError("bias_rope_kv: one inverse frequency a pair")
+    _req(positions, "positions", torch.int32, 1)
+    _req(token_req, "token_req", torch.int32, 1)
+    num_pages = max_blocks = 0
+    if k_pages is not None:
+        _req(k_pages, "k_pages", proj.dtype, 4)
+        _req(v_pages, "v_pages", proj.dtype, 4)
+        _req(block_table, "block_table", torch.int32, 2)
+        if tuple(k_pages.shape[1:]) != (nkv, page_size, d) or tuple(v_pages.shape) != (k_pages.shape[0], nkv, page_size, dv):
+            raise KernelError(f"bias_rope_kv: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not fit")
+        num_pages, max_blocks = k_pages.shape[0], block_table.shape[1]
+    _call("rope", "bias_rope_kv", library().qi_bias_rope_kv, _ptr(proj), C.c_longlong(proj.stride(0)), _ptr(bias), _ptr(q_out),
+          _code(proj), _ptr(inv_freq if rot else None), rot, int(bool(interleaved)), _ptr(positions), _ptr(token_req),
+          _ptr(block_table), max_blocks, page_size, num_pages, _ptr(k_pages), _ptr(v_pages), n, nq, nkv, d, dv, _ptr(status),
+          _stream())
+
+
+def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, slot_ids, heads: int, groups: int, P: int, N: int) -> None:
+    """The recurrence S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + d_skip x_t with
+    dt_t = softplus(raw_t + dt_bias), per head over each entry's tokens. xbc [n, heads P + 2 groups N] holds x | B | C;
+    raw_dt [n, heads] may be a block of columns of wider rows; state float32 [slots, heads, P, N] (read at an entry's first
+    token unless it starts its sequence, written after its last); y float32 [n, heads P]."""
+    for t, name in ((xbc, "xbc"), (raw_dt, "raw_dt")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"ssm_scan: {name} must be a CUDA tensor with contiguous rows")
+    if raw_dt.dtype != xbc.dtype or xbc.shape[1] != heads * P + 2 * groups * N or raw_dt.shape != (xbc.shape[0], heads):
+        raise KernelError("ssm_scan: the inputs do not fit the sizes")
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "a_log"), (d_skip, "d_skip")):
+        _req(t, name, torch.float32, 1)
+        if t.numel() != heads:
+            raise KernelError(f"ssm_scan: {name} needs one number a head")
+    _req_state(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, P, N):
+        raise KernelError(f"ssm_scan: state {tuple(state.shape)} does not fit [slots, {heads}, {P}, {N}]")
+    _req(y, "y", torch.float32, 2)
+    if tuple(y.shape) != (xbc.shape[0], heads * P):
+        raise KernelError("ssm_scan: y does not fit")
+    for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    _call("other", "ssm_scan", library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
+          C.c_longlong(raw_dt.stride(0)), _code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state),
+          C.c_longlong(state.stride(0)), _ptr(y), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, groups,
+          P, N, _stream())
+
+
+def gated_group_rmsnorm(y, z, gain, eps: float, out, groups: int) -> None:
+    """out = rmsnorm_groups(y * silu(z)) * gain: every width / groups coordinates by their own root mean square.
+    y float32 [n, width]; z [n, width] (may be a block of columns of wider rows); gain float32 [width]."""
+    _req(y, "y", torch.float32, 2)
+    if not z.is_cuda or z.dim() != 2 or z.stride(1) != 1 or z.shape != y.shape:
+        raise KernelError("gated_group_rmsnorm: z must match y, with contiguous rows")
+    _req(gain, "gain", torch.float32, 1)
+    _req(out, "out", ndim=2)
+    n, width = y.shape
+    if gain.numel() != width or out.shape != y.shape or groups <= 0 or width % groups:
+        raise KernelError("gated_group_rmsnorm: shapes do not agree")
+    _call("norm", "gated_group_rmsnorm", library().qi_gated_group_rmsnorm, _ptr(y), _ptr(z), _code(z), C.c_longlong(z.stride(0)),
+          _ptr(gain), C.c_float(eps), _ptr(out), _code(out), n, width, groups, _stream())
+
+
+def glu_clamped(gate_up, out, limit: float, alpha: float, interleaved: bool = False) -> None:
+    """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and up side by side
+    or interleaved in rows of gate_up [rows, 2 I]; out [rows, I]."""
+    _req(gate_up, "gate_up", ndim=2)
+    _req(out, "out", gate_up.dtype, 2)
+    rows, inter = out.shape
+    if tuple(gate_up.shape) != (rows, 2 * inter):
+        raise KernelError("glu_clamped: shapes do not agree")
+    _call("other", "glu_clamped", library().qi_glu_clamped, _ptr(gate_up), _ptr(out), _code(out), C.c_longlong(rows), inter,
+          int(bool(interleaved)), C.c_float(limit), C.c_float(alpha), _stream())
+
+
+def moe_tile_rows() -> int:
+    return int(library().qi_moe_tile_rows())
+
+
+def moe_route(logits, correction, ids, weights, scale: float) -> None:
+    """Per token: softmax over all experts, the `top` largest of softmax + correction, weights = the chosen experts' softmax
+    over their sum, times scale. logits float32 [n, E]; ids int32 [n, top]; weights float32 [n, top]."""
+    _req(logits, "logits", torch.float32, 2)
+    _req(ids, "ids", torch.int32, 2)
+    _req(weights, "weights", torch.float32, 2)
+    n, E = logits.shape
+    if ids.shape != weights.shape or ids.shape[0] != n:
+        raise KernelError("moe_route: shapes do not agree")
+    if correction is not None:
+        _req(correction, "correction", torch.float32, 1)
+        if correction.numel() != E:
+            raise KernelError("moe_route: one correction an expert")
+    _call("other", "moe_route", library().qi_moe_route, _ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, E,
+          ids.shape[1], C.c_float(scale), _stream())
+
+
+def moe_group(ids, n_experts: int, offsets, order, place, tiles) -> None:
+    """Sorts the (token, choice) pairs by expert on the device: offsets int32 [E + 1], order and place int32 [pairs],
+    tiles int32 [max_tiles, 3] (expert or -1, first sorted row, rows)."""
+    for t, name in ((ids, "ids"), (offsets, "offsets"), (order, "order"), (place, "place"), (tiles, "tiles")):
+        _req(t, name, torch.int32)
+    pairs = ids.numel()
+    if offsets.numel() != n_experts + 1 or order.numel() != pairs or place.numel() != pairs or tiles.dim() != 2 or tiles.shape[1] != 3:
+        raise KernelError("moe_group: shapes do not agree")
+    _call("other", "moe_group", library().qi_moe_group, _ptr(ids), pairs, n_experts, moe_tile_rows(), tiles.shape[0], _ptr(offsets),
+          _ptr(order), _ptr(place), _ptr(tiles), _stream())
+
+
+def moe_gemm(x, w, y, tiles, order, top: int, gather: bool) -> None:
+    """y[i] = w[expert of sorted row i] . x[order[i] // top if gather else i]. x [rows, K]; w [E, N, K]; y [pairs, N]."""
+    _req(x, "x", ndim=2)
+    _req(w, "w", ndim=3)
+    _req(y, "y", ndim=2)
+    _req(tiles, "tiles", torch.int32, 2)
+    _req(order, "order", torch.int32)
+    N, K = w.shape[1], w.shape[2]
+    if x.shape[1] != K or y.shape[1] != N:
+        raise KernelError(f"moe_gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _call("gemm", "moe_gemm", library().qi_moe_gemm, _ptr(x), _code(x), _ptr(w), _code(w), _ptr(y), _code(y), _ptr(tiles),
+          tiles.shape[0], _ptr(order), top, int(bool(gather)), N, K, C.c_longlong(K), C.c_longlong(N), _stream())
+
+
+def moe_combine(y, place, weights, shared, out) -> None:
+    """out[t] = sum_k weights[t, k] * y[place[t, k]] (+ shared[t]). y [n top, width]; out [n, width]."""
+    _req(y, "y", ndim=2)
+    _req(place, "place", torch.int32)
+    _req(weights, "weights", torch.float32, 2)
+    _req(out, "out", ndim=2)
+    n, top = weights.shape
+    width = out.shape[1]
+    if y.shape != (n * top, width) or out.shape[0] != n or place.numel() != n * top:
+        raise KernelError("moe_combine: shapes do not agree")
+    if shared is not None:
+        _req(shared, "shared", y.dtype, 2)
+        if shared.shape != out.shape:
+            raise KernelError("moe_combine: the shared output does not fit")
+    _call("other", "moe_combine", library().qi_moe_combine, _ptr(y), _code(y), _ptr(place), _ptr(weights), _ptr(shared), _ptr(out),
+          _code(out), n, top, width, _stream())
+
+
+def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv, scale: float, window: int, chunk: int, gate,
+                    status) -> None:
+    """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
+    kernel that fits the step."""
+    attention_generic(q, out, k_pages, v_pages, block_table, batch.positions, batch.token_req, nq, nkv, d, scale, window,
+                      status, chunk=chunk, gate=gate)

@@ -14,6 +14,8 @@ model it sits in. The interfaces:
   type, `batch` a :class:`StepBatch`, `cache` the :class:`CacheView` of the
   layer call;
 * feed-forward: `forward(x) -> y`;
+* a mixer may leave the bias of its last projection unapplied and offer it as `out_bias` (float32 [hidden] or
+  None): a block whose next norm can add it in its own pass does so, any other adds it at once;
 * block: `forward(resid, delta, batch, cache) -> (resid, delta)`: the 32-bit
   residual stream and the not-yet-added output of the last part.
 
@@ -50,7 +52,7 @@ import torch
 
 from ..errors import ConfigError
 
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "conv")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "conv", "reentry")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

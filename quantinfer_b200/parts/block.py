@@ -135,5 +135,59 @@ class ParallelGatedBlock(Part):
         return resid, out
 
 
+class SandwichBlock(Part):
+    """A norm before AND after each sublayer, and a multiplier on what joins the stream:
+
+        x = x + m * post1(mixer(pre1(x))) ;  x = x + m * post2(ffn(pre2(x)))
+
+    Nothing is added by a kernel of its own: a sublayer's output travels as a :class:`PostNormed` (with its
+    post-norm, the multiplier and the mixer's unapplied output bias) to the next pre-norm, in this block or the
+    next one, or to the model's final norm, which does post-norm, addition and its own norm in one pass when both
+    norms are elementwise (dynamic tanh). The feed-forward, with its two norms, may be absent."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.norm1 = build_part("norm", spec.mixer_norm, runtime)
+        self.norm1b = build_part("norm", spec.mixer_post_norm, runtime)
+        self.mixer = build_part("mixer", spec.mixer, runtime)
+        self.ffn = build_part("ffn", spec.ffn, runtime) if spec.ffn is not None else None
+        self.norm2 = build_part("norm", spec.ffn_norm, runtime) if spec.ffn is not None else None
+        self.norm2b = build_part("norm", spec.ffn_post_norm, runtime) if spec.ffn is not None else None
+        for n in (self.norm1b, self.norm2b):
+            if n is not None and not hasattr(n, "add_into"):
+                raise ConfigError("sandwich: a post-norm must be a norm that can be applied to a sublayer's output (add_into)")
+        self._parts = tuple(p for p in (self.norm1, self.norm1b, self.mixer, self.norm2, self.norm2b, self.ffn) if p is not None)
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        needs = {}
+        subs = [("norm", spec.mixer_norm), ("norm", spec.mixer_post_norm), ("mixer", spec.mixer)]
+        if spec.ffn is not None:
+            subs += [("norm", spec.ffn_norm), ("norm", spec.ffn_post_norm), ("ffn", spec.ffn)]
+        for cat, sub in subs:
+            needs.update(part_class(cat, sub).needs_of_spec(sub))
+        return needs
+
+    def load(self, tensors):
+        for p in self._parts:
+            p.load(tensors)
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, resid, delta, batch, cache):
+        from .norm import PostNormed
+
+        m = self.spec.residual_mult
+        h = self.norm1(resid, delta)
+        y = self.mixer.forward(h, batch, cache)
+        pending = PostNormed(y, self.norm1b, m, getattr(self.mixer, "out_bias", None))
+        if self.ffn is None:
+            return resid, pending
+        h = self.norm2(resid, pending)
+        return resid, PostNormed(self.ffn.forward(h), self.norm2b, m)
+
+
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "parallel_gated", ParallelGatedBlock)

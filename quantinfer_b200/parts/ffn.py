@@ -28,22 +28,24 @@ class GatedMLP(Part):
         self.gate_up = Linear(runtime, 2 * i, h, spec.prefix + "gate_up_proj")
         self.down = Linear(runtime, h, i, spec.prefix + "down_proj")
 
+    @staticmethod
+    def _names(spec):
+        gate, up, down = getattr(spec, "names", None) or ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+        return spec.prefix + gate, spec.prefix + up, spec.prefix + down
+
     @classmethod
     def needs_of_spec(cls, spec):
-        h, i, p = spec.hidden_size, spec.intermediate_size, spec.prefix
-        return {
-            p + "gate_proj.weight": TensorNeed((i, h)),
-            p + "up_proj.weight": TensorNeed((i, h)),
-            p + "down_proj.weight": TensorNeed((h, i)),
-        }
+        h, i = spec.hidden_size, spec.intermediate_size
+        gate, up, down = cls._names(spec)
+        return {gate: TensorNeed((i, h)), up: TensorNeed((i, h)), down: TensorNeed((h, i))}
 
     def load(self, tensors):
-        p = self.spec.prefix
-        g, u = tensors[p + "gate_proj.weight"], tensors[p + "up_proj.weight"]
+        gate, up, down = self._names(self.spec)
+        g, u = tensors[gate], tensors[up]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
         self.gate_up.load(torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]))
-        self.down.load(tensors[p + "down_proj.weight"])
+        self.down.load(tensors[down])
 
     def forward(self, x):
         return self.down(self.gate_up.forward_act_mul(x, self.spec.activation), keep_partials=True)

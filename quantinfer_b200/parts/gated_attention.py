@@ -1,0 +1,97 @@
+"""Causal grouped-query attention with biased projections, an output gate and chunks.
+
+    [q | k | v | g] = x . W^T                 (the four projections stacked at load: one product)
+    q, k            = rotate(q + b_q, p), rotate(k + b_k, p)      over the first `rotary_dim` coordinates of a head
+    cache[p]        = (k, v + b_v)            values may have another size than keys
+    a               = softmax(q k^T * scale over the visible keys) v
+    y               = (a * sigmoid(g)) . Wo^T (+ b_o)
+
+Visible keys of the query at position i: j <= i, within the last `window` positions if the spec has a window, and
+within i's own chunk (floor(i / chunk) = floor(j / chunk), chunks counted from the sequence's first position, not
+from where a step began) if it has chunks. The cache need carries both, so pages of chunks a request has left go
+back to the pool at once.
+
+The biases of q, k and v are added where the projection's row is read next (the rotation and cache-write kernel);
+the gate is applied where the attention's result is written; the output projection's bias is left unapplied and
+offered as `out_bias`, which a block's next norm adds in its own pass. Angles are computed where they are used,
+position * theta^(-2i / rotary_dim) in 32-bit: no table, no limit on positions.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.needs import PagedKVNeed
+from ..errors import ConfigError
+from ..weights.loader import TensorNeed
+from .base import Part, register_part
+from .linear import Linear
+
+
+class GatedAttention(Part):
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        s = spec
+        if s.num_heads % s.num_kv_heads:
+            raise ConfigError(f"{s.num_heads} query heads are not a multiple of {s.num_kv_heads} kv heads")
+        for name, v in (("window", s.window), ("chunk", s.chunk)):
+            if v is not None and v <= 0:
+                raise ConfigError(f"gated_attention: {name} must be positive or None")
+        self.H, self.G, self.d, self.dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
+        self.qkv_cols = (self.H + self.G) * self.d + self.G * self.dv
+        self.proj = Linear(runtime, self.qkv_cols + (self.H * self.dv if s.out_gate else 0), s.hidden_size, s.prefix + "q+k+v+g")
+        self.o = Linear(runtime, s.hidden_size, self.H * self.dv, s.prefix + "o")
+        self.bias = self.out_bias = self.inv_freq = None
+        pos = s.position
+        self.rot = pos.rotary_dim if pos is not None else 0
+        self.interleaved = pos is not None and pos.pairing == "interleaved"
+        if pos is not None:
+            if pos.pairing not in ("half_split", "interleaved") or pos.rotary_dim % 2 or not 0 < pos.rotary_dim <= s.head_dim:
+                raise ConfigError(f"gated_attention: a rotation over {pos.rotary_dim} of {s.head_dim} coordinates ({pos.pairing})")
+            exponent = (2.0 * torch.arange(self.rot // 2, dtype=torch.float64)) / float(self.rot)
+            self.inv_freq = torch.pow(torch.tensor(float(pos.theta), dtype=torch.float64), -exponent).to(torch.float32).to(runtime.device)
+
+    @classmethod
+    def needs_of_spec(cls, s):
+        p, H, G, d, dv, w = s.prefix, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, s.hidden_size
+        needs = {p + "q": TensorNeed((H * d, w)), p + "k": TensorNeed((G * d, w)), p + "v": TensorNeed((G * dv, w))}
+        if s.out_gate:
+            needs[p + "g"] = TensorNeed((H * dv, w))
+        needs[p + "o"] = TensorNeed((w, H * dv))
+        if s.bias:
+            needs.update({p + "q.b": TensorNeed((H * d,), "matrix", "zeros"), p + "k.b": TensorNeed((G * d,), "matrix", "zeros"),
+                          p + "v.b": TensorNeed((G * dv,), "matrix", "zeros"), p + "o.b": TensorNeed((w,), "matrix", "zeros")})
+        return needs
+
+    def load(self, tensors):
+        p, s = self.spec.prefix, self.spec
+        ws = [tensors[p + n] for n in ("q", "k", "v") + (("g",) if s.out_gate else ())]
+        if len({t.dtype for t in ws}) > 1:
+            ws = [t.to(torch.float32) for t in ws]
+        self.proj.load(torch.cat(ws, dim=0))
+        self.o.load(tensors[p + "o"])
+        if s.bias:
+            self.bias = self._gain(torch.cat([tensors[p + n + ".b"].to(torch.float32) for n in ("q", "k", "v")]))
+            self.out_bias = self._gain(tensors[p + "o.b"])
+
+    def cache_need(self):
+        return PagedKVNeed(self.G, self.d, self.spec.window, self.dv if self.dv != self.d else None, self.spec.chunk)
+
+    def forward(self, x, batch, cache):
+        rt, s = self.runtime, self.spec
+        n = x.shape[0]
+        table = batch.block_tables[cache.group]
+        proj = self.proj(x)
+        q = torch.empty((n, self.H * self.d), dtype=x.dtype, device=x.device)
+        kernels.bias_rope_kv(proj, self.bias, q, self.inv_freq, self.rot, self.interleaved, batch.positions, batch.token_req,
+                             table, cache.page_size, cache.k_pages if cache.writes else None,
+                             cache.v_pages if cache.writes else None, self.H, self.G, self.d, self.dv, rt.status)
+        out = torch.empty((n, self.H * self.dv), dtype=x.dtype, device=x.device)
+        gate = proj[:, self.qkv_cols:] if s.out_gate else None
+        kernels.gated_attention(q, out, cache.k_pages, cache.v_pages, table, batch, self.H, self.G, self.d, self.dv, s.scale,
+                                s.window or 0, s.chunk or 0, gate, rt.status)
+        return self.o(out)
+
+
+register_part("mixer", "gated_attention", GatedAttention)

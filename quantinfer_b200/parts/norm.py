@@ -28,6 +28,29 @@ def sum_partials(delta, dtype=None):
     return total if dtype is None else total.to(dtype)
 
 
+class PostNormed:
+    """A sublayer's output that has not joined the residual stream yet: the stream is to receive
+    `mult * post(y + bias)`, `post` a norm applied AFTER the sublayer (None: y + bias as it is). A block hands
+    this on as its `delta`, so that the next norm's kernel does the post-norm, the addition and its own norm in one
+    pass; `apply` does the addition alone, for whoever cannot fuse it."""
+
+    def __init__(self, y, post=None, mult: float = 1.0, bias=None):
+        self.y, self.post, self.mult, self.bias = y, post, mult, bias
+
+    def apply(self, resid):
+        """resid += mult * post(y + bias); returns None (nothing is pending any more)."""
+        if self.post is not None:
+            self.post.add_into(resid, self.y, self.bias, self.mult)
+        else:
+            kernels.dyt(resid, self.y, self.bias)
+        return None
+
+
+def settle(resid, delta):
+    """`delta` as something every norm takes: a pending :class:`PostNormed` is added to the stream now."""
+    return delta.apply(resid) if isinstance(delta, PostNormed) else delta
+
+
 class RMSNorm(Part):
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -41,6 +64,7 @@ class RMSNorm(Part):
         self.gain = self._gain(tensors[self.spec.prefix + "weight"])
 
     def forward(self, resid, delta, rows=None, write_resid=True):
+        delta = settle(resid, delta)
         n = resid.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
         kernels.add_rmsnorm(resid, delta, self.gain, self.spec.eps, out, rows=rows, write_resid=write_resid)
@@ -63,5 +87,56 @@ class ScalarRMSNorm(RMSNorm):
         self.gain = self._gain(g.expand(self.spec.size))
 
 
+class DynamicTanh(Part):
+    """Dynamic tanh in the place of a norm: out = tanh(alpha x) w + b, elementwise, with no mean or variance of the
+    row (the spec's eps is unused). w is the tensor named by the spec's `prefix` itself, b `prefix.b`, alpha
+    `prefix.alpha` of shape []; all are used in 32-bit, alpha from device memory. Being elementwise, it fuses with
+    everything around it: as a pre-norm it takes the pending output of the sublayer before it (`delta`, plain or a
+    :class:`PostNormed` with ITS post-norm, multiplier and unapplied bias), adds it to the stream and normalises the
+    result in one launch; as a post-norm it is applied by whoever consumes the `PostNormed` that names it."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.w = self.b = self.alpha = None
+
+    @classmethod
+    def needs_of_spec(cls, spec):
+        p = spec.prefix
+        return {p: TensorNeed((spec.size,), "gain", "gain"), p + ".b": TensorNeed((spec.size,), "gain", "zeros"),
+                p + ".alpha": TensorNeed((), "gain", "gain")}
+
+    def load(self, tensors):
+        p = self.spec.prefix
+        self.w, self.b = self._gain(tensors[p]), self._gain(tensors[p + ".b"])
+        self.alpha = self._gain(tensors[p + ".alpha"].reshape(1))
+
+    def params(self):
+        return (self.w, self.b, self.alpha)
+
+    def add_into(self, resid, y, bias=None, mult: float = 1.0):
+        """resid += mult * dyt(y + bias)."""
+        kernels.dyt(resid, y, bias, post=self.params(), mult=mult)
+
+    def forward(self, resid, delta, rows=None, write_resid=True):
+        n = resid.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.spec.size), dtype=self.runtime.dtype, device=resid.device)
+        y = bias = post = None
+        mult = 1.0
+        if isinstance(delta, PostNormed):
+            if delta.post is not None and not isinstance(delta.post, DynamicTanh):
+                delta = delta.apply(resid)        # a post-norm of another kind cannot ride in this kernel
+            else:
+                y, bias, mult = delta.y, delta.bias, delta.mult
+                post = delta.post.params() if delta.post is not None else None
+        if delta is not None and not isinstance(delta, PostNormed):
+            y = sum_partials(delta)
+        kernels.dyt(resid, y, bias, post=post, mult=mult, pre=self.params(), out=out, rows=rows,
+                    write_resid=write_resid and rows is None)
+        return out
+
+    __call__ = forward
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "dyt", DynamicTanh)
 register_part("norm", "rmsnorm_scalar", ScalarRMSNorm)
