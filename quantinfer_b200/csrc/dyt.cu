@@ -10,7 +10,8 @@
 //     t = y + y_bias ;  t = mult * dyt_post(t)  (when a post-norm is given) ;  x = resid + t ;  resid = x
 //     out = dyt_pre(x)                           (when a pre-norm is given)
 //
-// `rows` gathers source rows (the head reads only the wanted places; the stream is then not written).
+// y may also be the 32-bit partial sums [splits, n, h] of a projection whose product was cut along K; they are
+// added here, in split order. `rows` gathers source rows (the head reads only the wanted places; the stream is then not written).
 // All arithmetic is 32-bit; y and out may be bfloat16. alpha is read from device memory (a tensor of
 // shape []), so nothing crosses to the host.
 #include "common.cuh"
@@ -19,7 +20,7 @@ namespace {
 
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(256)
-dyt_kernel(float* __restrict__ resid, const TY* __restrict__ y, const float* __restrict__ y_bias,
+dyt_kernel(float* __restrict__ resid, const TY* __restrict__ y, int splits, long long split_stride, const float* __restrict__ y_bias,
            const float* __restrict__ post_w, const float* __restrict__ post_b, const float* __restrict__ post_alpha,
            float mult, const float* __restrict__ pre_w, const float* __restrict__ pre_b,
            const float* __restrict__ pre_alpha, TO* __restrict__ out, const int* __restrict__ rows, int n_out, int h,
@@ -35,6 +36,7 @@ dyt_kernel(float* __restrict__ resid, const TY* __restrict__ y, const float* __r
         float x = resid[src];
         if (y) {
             float t = qi::to_f32<TY>(y[src]);
+            for (int sp = 1; sp < splits; ++sp) t += qi::to_f32<TY>(y[(size_t)sp * split_stride + src]);
             if (y_bias) t += y_bias[c];
             if (post_w) t = mult * (tanhf(pa * t) * post_w[c] + post_b[c]);
             x += t;
@@ -63,10 +65,11 @@ unsigned blocks_for(size_t total) {
 
 }  // namespace
 
-// resid float32 [n, h] (rows picked by `rows` when given); y [n, h] in y_dtype or null; y_bias float32 [h] or null;
+// resid float32 [n, h] (rows picked by `rows` when given); y [n, h] in y_dtype (or `splits` such arrays, `split_stride`
+// elements apart) or null; y_bias float32 [h] or null;
 // post_w / post_b float32 [h] and post_alpha float32 [1] or all null (then y is added as it is); pre_* likewise with
 // out [n_out, h] in out_dtype, or all null with out null.
-extern "C" int qi_dyt(float* resid, const void* y, int y_dtype, const float* y_bias, const float* post_w,
+extern "C" int qi_dyt(float* resid, const void* y, int y_dtype, int splits, long long split_stride, const float* y_bias, const float* post_w,
                       const float* post_b, const float* post_alpha, float mult, const float* pre_w, const float* pre_b,
                       const float* pre_alpha, void* out, int out_dtype, const int* rows, int n_out, int h,
                       int write_resid, cudaStream_t stream) {
@@ -81,7 +84,7 @@ extern "C" int qi_dyt(float* resid, const void* y, int y_dtype, const float* y_b
     const dim3 grid(blocks_for((size_t)n_out * h)), block(256);
     QI_DISPATCH_DTYPE(y ? y_dtype : qi::kF32, TY, {
         QI_DISPATCH_DTYPE(out ? out_dtype : qi::kF32, TO, {
-            qi::launch(dyt_kernel<TY, TO>, grid, block, 0, stream, resid, (const TY*)y, y_bias, post_w, post_b, post_alpha, mult,
+            qi::launch(dyt_kernel<TY, TO>, grid, block, 0, stream, resid, (const TY*)y, splits, split_stride, y_bias, post_w, post_b, post_alpha, mult,
                        pre_w, pre_b, pre_alpha, (TO*)out, rows, n_out, h, write_resid);
         });
     });

@@ -51,8 +51,6 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
         c[i] = e < E ? s[i] + (correction ? correction[e] : 0.f) : -INFINITY;
     }
     float chosen_sum = 0.f;
-    float my_w = 0.f;      // lane k keeps the k-th choice's score
-    int my_id = 0;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int best_e = 0x7fffffff;
@@ -73,13 +71,13 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
             if (lane + 32 * i == best_e) { sc = s[i]; c[i] = -INFINITY; }
         sc = qi::warp_sum(sc);
         chosen_sum += sc;
-        if (k == lane) { my_w = sc; my_id = best_e; }      // lane k keeps choice k (top <= 32)
+        if ((k & 31) == lane) {      // lane k mod 32 writes choice k and scales it below
+            ids[(size_t)t * top + k] = best_e;
+            weights[(size_t)t * top + k] = sc;
+        }
     }
     const float inv = scale / (chosen_sum + 1e-20f);
-    if (lane < top) {
-        ids[(size_t)t * top + lane] = my_id;
-        weights[(size_t)t * top + lane] = my_w * inv;
-    }
+    for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= inv;
 }
 
 // One block. smem: counts[E], offsets[E + 1], tile_base[E + 1].
@@ -223,7 +221,6 @@ extern "C" int qi_moe_route(const float* logits, const float* correction, int* i
                             float scale, cudaStream_t stream) {
     QI_REQUIRE(n >= 0 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes n=%d experts=%d top=%d", n, E, top);
     QI_REQUIRE(E <= 32 * kMaxPerLane, "moe_route: %d experts are above this kernel's %d", E, 32 * kMaxPerLane);
-    QI_REQUIRE(top <= 32, "moe_route: %d choices a token are above this kernel's 32", top);
     if (n == 0) return 0;
     qi::launch(moe_route_kernel, dim3((n + 3) / 4), dim3(128), 0, stream, logits, correction, ids, weights, n, E, top, scale);
     return qi::check_launch("moe_route");

@@ -1002,13 +1002,17 @@ def latent_attention(q, out, cache, sink, block_table, q_start, start_pos, posit
 def dyt(resid, y=None, y_bias=None, post=None, mult: float = 1.0, pre=None, out=None, rows=None, write_resid: bool = True) -> None:
     """The elementwise work around a sublayer of a model normalised by dynamic tanh, dyt(v) = tanh(alpha v) w + b:
     resid += mult * dyt_post(y + y_bias) (or resid += y + y_bias without `post`), then out = dyt_pre(resid).
-    resid float32 [n, h]; y [n, h] or None; y_bias float32 [h] or None; post, pre: (w, b, alpha) float32 [h], [h], [1]
+    resid float32 [n, h]; y [n, h] (or the partial sums [splits, n, h] of a K-split product, added here) or None;
+    y_bias float32 [h] or None; post, pre: (w, b, alpha) float32 [h], [h], [1]
     or None; out [n, h] (or [len(rows), h] when `rows` picks source rows; the stream is then not written)."""
     _req(resid, "resid", torch.float32, 2)
     n, h = resid.shape
+    splits, stride = 1, 0
     if y is not None:
-        _req(y, "y", ndim=2)
-        if tuple(y.shape) != (n, h):
+        _req(y, "y")
+        if y.dim() == 3:
+            splits, stride = y.shape[0], y.shape[1] * y.shape[2]
+        if tuple(y.shape[-2:]) != (n, h) or y.dim() not in (2, 3):
             raise KernelError(f"dyt: y {tuple(y.shape)} does not match resid {tuple(resid.shape)}")
     for trio, name in ((post, "post"), (pre, "pre")):
         if trio is not None:
@@ -1034,8 +1038,8 @@ def dyt(resid, y=None, y_bias=None, post=None, mult: float = 1.0, pre=None, out=
             raise KernelError(f"dyt: out is {tuple(out.shape)}, expected {(n_out, h)}")
     pw, pb, pa = post if post is not None else (None, None, None)
     rw, rb, ra = pre if pre is not None else (None, None, None)
-    _call("norm", "dyt", library().qi_dyt, _ptr(resid), _ptr(y), _code(y) if y is not None else F32, _ptr(y_bias),
-          _ptr(pw), _ptr(pb), _ptr(pa), C.c_float(mult), _ptr(rw), _ptr(rb), _ptr(ra), _ptr(out),
+    _call("norm", "dyt", library().qi_dyt, _ptr(resid), _ptr(y), _code(y) if y is not None else F32, splits, C.c_longlong(stride),
+          _ptr(y_bias), _ptr(pw), _ptr(pb), _ptr(pa), C.c_float(mult), _ptr(rw), _ptr(rb), _ptr(ra), _ptr(out),
           _code(out) if out is not None else F32, _ptr(rows), n_out, h, int(bool(write_resid)), _stream())
 
 

@@ -91,7 +91,7 @@ class GatedAttention(Part):
         gate = proj[:, self.qkv_cols:] if s.out_gate else None
         kernels.gated_attention(q, out, cache.k_pages, cache.v_pages, table, batch, self.H, self.G, self.d, self.dv, s.scale,
                                 s.window or 0, s.chunk or 0, gate, rt.status)
-        return self.o(out)
+        return self.o(out, keep_partials=True)
 
 
 register_part("mixer", "gated_attention", GatedAttention)

@@ -80,7 +80,7 @@ class Mamba2(Part):
                          batch.q_start, batch.start_pos, batch.slot_ids, s.heads, s.groups, s.head_dim, s.state)
         g = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_rmsnorm(y, proj[:, :self.inner], self.gain, s.norm_eps, g, s.norm_groups)
-        return self.o(g)
+        return self.o(g, keep_partials=True)
 
 
 register_part("mixer", "mamba2", Mamba2)

@@ -129,7 +129,7 @@ class DynamicTanh(Part):
                 y, bias, mult = delta.y, delta.bias, delta.mult
                 post = delta.post.params() if delta.post is not None else None
         if delta is not None and not isinstance(delta, PostNormed):
-            y = sum_partials(delta)
+            y = delta
         kernels.dyt(resid, y, bias, post=post, mult=mult, pre=self.params(), out=out, rows=rows,
                     write_resid=write_resid and rows is None)
         return out

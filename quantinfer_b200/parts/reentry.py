@@ -14,7 +14,7 @@ from .. import kernels
 from ..weights.loader import TensorNeed
 from .base import Part, register_part
 from .linear import Linear
-from .norm import PostNormed, sum_partials
+from .norm import PostNormed
 
 
 class ConcatProjection(Part):
@@ -33,7 +33,7 @@ class ConcatProjection(Part):
         if isinstance(delta, PostNormed):
             delta = delta.apply(resid)
         if delta is not None:
-            kernels.dyt(resid, sum_partials(delta))
+            kernels.dyt(resid, delta)
         both = torch.empty((resid.shape[0], 2 * self.spec.hidden_size), dtype=self.runtime.dtype, device=resid.device)
         kernels.concat_cast(resid, x0, both)
         return self.proj(both, out_dtype=torch.float32)

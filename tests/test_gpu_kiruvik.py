@@ -1,0 +1,410 @@
+"""The Kiruvik design on the GPU against the plain implementation (tests/plain/plain_kiruvik.py): every mechanism
+alone, then whole models replayed whole, token by token, in portions down to two tokens and mixed with other
+requests on a pool so small that pages and slots are used again; generation through the scheduler.
+
+Where random weights would hide a fault the inputs are made so that it shows: one key whose score stands out for
+every query of its chunk and for none of the next, a recurrent state carried over a hundred steps, a slot whose
+earlier owner left its state behind, routers with clear winners."""
+
+import json
+import math
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import random_tokens
+from kiruvik_tools import CONFIGS, PAGE_SIZES, attn, dense, draw_weights, layer, make, moe, plain_rows, ssm, write_folder
+from plain import plain_kiruvik as plain
+from trace_tools import ROOT, collect, mixed_trace, portions_trace, round64, run_trace_engine, tail_trace, whole_trace
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+# |engine - plain float64| on logits of a few units. float32: the order of sums and the device's exp, tanh, sin, cos.
+# bfloat16: three times the error that most rows show; a token whose router has two experts within rounding of each
+# other may take the other one in bfloat16, so a few rows of a hundred may lie beyond it (never in float32).
+TOL_F32 = 2e-5
+TOL_BF16 = {"P": 0.12, "Q": 0.2, "R": 0.12}
+BF16_ROWS_BEYOND = 0.04
+LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 150, 5], "R": [50, 33, 80, 17, 64, 9]}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("kiruvik")
+    return {name: make(root / name, name) for name in CONFIGS}
+
+
+def _requests(name):
+    v = CONFIGS[name]["vocab"]
+    return {f"{name}{i}": random_tokens(n, v, seed=37 * i + n) for i, n in enumerate(LENGTHS[name])}
+
+
+_expected = {}
+
+
+def _expect(models, name):
+    if name not in _expected:
+        _, cfg, w = models[name]
+        _expected[name] = plain_rows(cfg, w, _requests(name))
+    return _expected[name]
+
+
+def _compare(got, expect, name, dtype, what=""):
+    assert set(got) == set(expect)
+    errs = {k: float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect}
+    worst = max(errs, key=errs.get)
+    if dtype == "float32":
+        print(f"measured {name} {dtype} {what}: {errs[worst]:.3g} at {worst}")
+        assert errs[worst] <= TOL_F32, f"worst difference {errs[worst]} at (request, position) {worst}"
+        return
+    beyond = sorted(k for k in errs if errs[k] > TOL_BF16[name])
+    print(f"measured {name} {dtype} {what}: median {np.median(list(errs.values())):.3g}, worst {errs[worst]:.3g}, {len(beyond)} of {len(errs)} beyond")
+    assert len(beyond) <= BF16_ROWS_BEYOND * len(errs), (len(beyond), len(errs), beyond[:5])
+
+
+# ---------------------------------------------------------------- small kernels against their formulas
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dynamic_tanh_with_the_residual_update_fused_in(dtype):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(0)
+    n, h = 37, 44
+    resid = torch.randn(n, h)
+    y = torch.randn(n, h).to(dtype)
+    bias = torch.randn(h) * 0.3
+    post = (torch.randn(h), torch.randn(h) * 0.2, torch.tensor([0.7]))
+    pre = (torch.randn(h), torch.randn(h) * 0.2, torch.tensor([1.3]))
+    dy = lambda v, t: torch.tanh(t[2].double() * v) * t[0].double() + t[1].double()
+    x_ref = resid.double() + 0.6 * dy(y.double() + bias.double(), post)
+    out_ref = dy(x_ref, pre)
+    d = lambda t: t.to(DEV)
+    r = d(resid.clone())
+    out = torch.empty(n, h, dtype=dtype, device=DEV)
+    k.dyt(r, d(y), d(bias), post=tuple(map(d, post)), mult=0.6, pre=tuple(map(d, pre)), out=out)
+    assert float((r.cpu().double() - x_ref).abs().max()) < 2e-6
+    assert float((out.cpu().double() - out_ref).abs().max()) < (3e-6 if dtype == torch.float32 else 0.03)
+    # picked rows: the stream is read, not written; a plain delta without a post-norm
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32)
+    r2 = d(resid.clone())
+    out2 = torch.empty(4, h, dtype=dtype, device=DEV)
+    k.dyt(r2, d(y), None, pre=tuple(map(d, pre)), out=out2, rows=d(rows))
+    assert torch.equal(r2.cpu(), resid)
+    ref2 = dy(resid.double() + y.double(), pre)[rows.long()]
+    assert float((out2.cpu().double() - ref2).abs().max()) < (3e-6 if dtype == torch.float32 else 0.03)
+    # the addition alone
+    r3 = d(resid.clone())
+    k.dyt(r3, d(y), d(bias))
+    assert float((r3.cpu().double() - (resid.double() + y.double() + bias.double())).abs().max()) < 1e-6
+    both = torch.empty(n, 2 * h, dtype=dtype, device=DEV)
+    k.concat_cast(r3, d(resid), both)
+    assert torch.equal(both.cpu(), torch.cat([r3.cpu(), resid], dim=1).to(dtype))
+
+
+@pytest.mark.parametrize("E, top", [(5, 3), (8, 1), (64, 6), (33, 33), (200, 4)])
+def test_router_choice_and_weights(E, top):
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(E)
+    n = 50
+    logits = torch.randn(n, E) * 3.0
+    corr = torch.randn(E) * 0.2
+    s = torch.softmax(logits.double(), dim=-1)
+    idx = torch.topk(s + corr.double(), top, dim=-1).indices
+    sel = torch.gather(s, 1, idx)
+    wref = sel / (sel.sum(dim=1, keepdim=True) + 1e-20) * 1.7
+    ids = torch.empty(n, top, dtype=torch.int32, device=DEV)
+    wts = torch.empty(n, top, dtype=torch.float32, device=DEV)
+    k.moe_route(logits.to(DEV), corr.to(DEV), ids, wts, 1.7)
+    assert torch.equal(ids.cpu().long(), idx)
+    assert float((wts.cpu().double() - wref).abs().max()) < 2e-6
+    # grouping: every pair once, sorted by expert, tiles that no two experts share
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    order = torch.empty(n * top, dtype=torch.int32, device=DEV)
+    place = torch.empty(n * top, dtype=torch.int32, device=DEV)
+    tiles = torch.empty((min(n * top, n * top // k.moe_tile_rows() + E), 3), dtype=torch.int32, device=DEV)
+    k.moe_group(ids, E, offsets, order, place, tiles)
+    offsets, order, place, tiles = offsets.cpu(), order.cpu().long(), place.cpu().long(), tiles.cpu()
+    flat = ids.cpu().flatten().long()
+    assert offsets.tolist() == [0] + torch.cumsum(torch.bincount(flat, minlength=E), 0).tolist()
+    assert sorted(order.tolist()) == list(range(n * top)) and torch.equal(order[place], torch.arange(n * top))
+    assert torch.equal(flat[order], torch.sort(flat).values)
+    covered = []
+    for e, r0, rows in tiles.tolist():
+        if e >= 0:
+            assert offsets[e] <= r0 and r0 + rows <= offsets[e + 1] and 0 < rows <= k.moe_tile_rows()
+            covered += list(range(r0, r0 + rows))
+    assert sorted(covered) == list(range(n * top))
+
+
+# ---------------------------------------------------------------- one mixer or feed-forward alone, in an engine of one layer
+
+
+def _one_layer(tmp_path, entry, width, dtype, page_size=8, seed=77, eps=1e-6, max_tokens=512):
+    from quantinfer_b200.engine import Engine
+
+    cfg = {"architecture": "Kiruvik", "vocab": 16, "width": width, "norm": {"eps": eps}, "residual_mult": 1.0, "layers": [entry]}
+    w = draw_weights(cfg, seed)
+    folder = write_folder(tmp_path / f"one{dtype}{seed}", cfg, w)
+    eng = Engine.from_folder(folder, dtype=dtype, page_size=page_size, max_tokens=max_tokens, max_requests=4, use_graphs=False)
+    return eng, cfg, {k: v.double() for k, v in w.items()}
+
+
+def _run_mixer(eng, inputs, cuts, rid="r"):
+    """Feeds `inputs` [T, width] through the layer's mixer in portions `cuts` for one request."""
+    from quantinfer_b200.engine import StepEntry
+
+    eng.open(rid)
+    outs, a = [], 0
+    mixer = eng.model.blocks[0].mixer
+    for n in cuts:
+        eng.cache.prepare(rid, n)
+        batch = eng.make_batch([StepEntry(rid, [0] * n, [])])
+        y = mixer.forward(inputs[a:a + n].to(DEV, eng.dtype), batch, eng._views[0]).float()
+        if y.dim() == 3:            # the partial sums of a projection cut along K
+            y = y.sum(dim=0)
+        if getattr(mixer, "out_bias", None) is not None:
+            y = y + mixer.out_bias
+        outs.append(y.cpu())
+        eng.raise_on_status()
+        eng.cache.commit(rid)
+        a += n
+    eng.close(rid)
+    return torch.cat(outs)
+
+
+def _cycle(T, sizes):
+    out, i = [], 0
+    while sum(out) < T:
+        out.append(min(sizes[i % len(sizes)], T - sum(out)))
+        i += 1
+    return out
+
+
+CUTS = {"whole": lambda T: [T], "one by one": lambda T: [1] * T,
+        "portions": lambda T: _cycle(T, (2, 7, 3, 16, 2, 5, 31, 1)), "prompt then decode": lambda T: [T - 20] + [1] * 20}
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("chunk", [None, 9, 16, 17])
+def test_a_dominant_key_and_the_chunks_edges_show_in_the_mixer(tmp_path, cut, chunk):
+    """One position's input is scaled so that its key gives by far the largest score, of either sign, to every
+    query that sees it: the later positions of its own chunk and none of the next (without chunks: every later
+    position). It stands at the last row of a page. A chunk counted from a step's first token instead of the
+    sequence's, a bound one off, a key lost at a page's border or a stale page changes rows by far more than the
+    bound; values are smaller than keys here and three query heads share each kv head."""
+    entry = layer(attn(6, 2, 10, 6, 6, chunk=chunk, base=100.0, scale=0.3), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", page_size=8)
+    T, far = 75, 23
+    torch.manual_seed(3)
+    x = torch.randn(T, 24) * 0.5
+    x[far] *= 25.0
+    ref = plain.gated_attention(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    got = _run_mixer(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+    # the premise: hiding the far key changes the rows of its chunk that follow it, and only those
+    x2 = x.clone()
+    x2[far] = 0.0
+    ref2 = plain.gated_attention(x2.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    moved = ((ref - ref2).abs().max(dim=1).values > 0.05).nonzero().flatten().tolist()
+    last = T - 1 if chunk is None else min(T - 1, (far // chunk + 1) * chunk - 1)
+    assert moved and set(moved) <= set(range(far, last + 1)) and len(moved) >= (last - far + 1) // 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_rounds_only_where_it_may(tmp_path, dtype):
+    """The whole head rotated, one kv head, keys smaller than values, positions beyond a thousand (angles in 32-bit)."""
+    from quantinfer_b200.engine import StepEntry
+
+    entry = layer(attn(4, 1, 16, 32, 16, chunk=64, base=20000.0), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, dtype, page_size=16, seed=5, max_tokens=1152)
+    T = 1100
+    torch.manual_seed(6)
+    x = (torch.randn(T, 32) * 0.7).to(torch.bfloat16).float()
+    ref = plain.gated_attention(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    got = _run_mixer(eng, x, [1000, 37] + [1] * 63)
+    err = float((got.double() - ref).abs().max())
+    assert err < (1e-4 if dtype == "float32" else 0.06), err
+
+
+@pytest.mark.parametrize("cut", list(CUTS))
+@pytest.mark.parametrize("shape", [(4, 6, 5, 2, 4, 3), (2, 32, 64, 1, 2, 1), (3, 8, 33, 3, 1, 1), (1, 20, 16, 1, 3, 2)])
+def test_the_recurrent_mixer_however_the_sequence_is_cut(tmp_path, cut, shape):
+    """heads, channels a head, state rows, groups, taps, norm parts. The slot's earlier owner leaves its state behind."""
+    entry = layer(ssm(*shape), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", seed=9, eps=2e-6)
+    T = 75
+    torch.manual_seed(4)
+    x = torch.randn(T, 24)
+    _run_mixer(eng, torch.randn(40, 24) * 3.0, [40], rid="earlier")
+    ref = plain.mamba2(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 2e-6)
+    got = _run_mixer(eng, x, CUTS[cut](T))
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+    # the premise: the state matters (a row depends on an input twenty positions back, beyond any convolution)
+    x2 = x.clone()
+    x2[20] += 1.0
+    ref2 = plain.mamba2(x2.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 2e-6)
+    assert float((ref2[40] - ref[40]).abs().max()) > 1e-3
+
+
+def test_the_recurrent_state_over_three_hundred_single_steps_in_bfloat16(tmp_path):
+    entry = layer(ssm(2, 16, 16, 1, 4, 1), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 32, "bfloat16", seed=10)
+    T = 320
+    torch.manual_seed(5)
+    x = torch.randn(T, 32).to(torch.bfloat16).float()
+    ref = plain.mamba2(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 1e-6)
+    got = _run_mixer(eng, x, [3] + [1] * (T - 3))
+    whole = _run_mixer(eng, x, [T])
+    assert float((got.double() - ref).abs().max()) < 0.08 and float((whole.double() - ref).abs().max()) < 0.08
+    assert float((got[-50:] - whole[-50:]).abs().max()) < 0.05       # no drift between the two ways to get there
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mlp", [moe(5, 3, 1.7, 12, 0.8, shared=(20, 1.3)), moe(8, 1, 2.0, 32, 1.0), moe(3, 3, 0.9, 10, 2.0),
+                                 moe(40, 4, 1.0, 8, 1.0, shared=(8, 0.5)), dense(56)])
+def test_feed_forwards_alone_and_a_token_in_any_company(tmp_path, dtype, mlp):
+    entry = layer(attn(2, 1, 8, 8, 0), mlp)
+    eng, cfg, w = _one_layer(tmp_path, entry, 40, dtype, seed=12)
+    ffn = eng.model.blocks[0].ffn
+    torch.manual_seed(7)
+    x = (torch.randn(150, 40)).to(torch.bfloat16).float()
+    ref = plain.dense_ffn(x.double(), w, "l0.mlp.") if mlp["kind"] == "dense" else plain.moe(x.double(), mlp, w, "l0.mlp.")
+    xd = x.to(DEV, eng.dtype)
+    got = ffn.forward(xd).float().cpu()
+    if got.dim() == 3:
+        got = got.sum(dim=0)
+    err = (got.double() - ref).abs().max(dim=1).values
+    if dtype == "float32":
+        assert float(err.max()) < 5e-5, (int(err.argmax()), float(err.max()))
+    else:
+        assert float(err.median()) < 0.03 and int((err > 0.1).sum()) <= 6, (float(err.median()), int((err > 0.1).sum()))
+    if mlp["kind"] == "moe":
+        # the same token alone, among three and among all: bit for bit the same
+        alone = torch.cat([ffn.forward(xd[i:i + 1]) for i in (0, 77, 149)]).float().cpu()
+        few = ffn.forward(xd[[0, 77, 149]]).float().cpu()
+        assert torch.equal(alone, got[[0, 77, 149]]) and torch.equal(few, alone)
+        # the limits matter in this test
+        loose = dict(mlp, expert=dict(mlp["expert"], limit=1e9))
+        assert float((plain.moe(x.double(), loose, w, "l0.mlp.") - ref).abs().max()) > 0.01
+
+
+# ---------------------------------------------------------------- whole models, replayed
+
+
+def _family(name, reqs, family):
+    longest = round64(max(LENGTHS[name]))
+    if family == "whole":
+        return whole_trace(reqs), longest
+    if family == "tail":
+        return tail_trace(reqs, 48), longest
+    if family == "portions":
+        return portions_trace(reqs), longest
+    steps, peak = mixed_trace(reqs, seed=5, max_live=4, max_tokens=longest + 2 * 64)
+    assert sum(round64(n) for n in LENGTHS[name]) > peak and max(len(s["entries"]) for s in steps) >= 3
+    return steps, peak
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("family", ["whole", "tail", "portions", "mixed"])
+def test_replay_family(models, name, dtype, family):
+    folder, cfg, w = models[name]
+    steps, max_tokens = _family(name, _requests(name), family)
+    got = run_trace_engine(folder, dtype, steps, max_tokens, PAGE_SIZES[name])
+    _compare(got, _expect(models, name), name, dtype, family)
+
+
+def test_the_cuts_agree_with_one_another_bit_for_bit_in_float32(models):
+    """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
+    folder, cfg, w = models["P"]
+    reqs = _requests("P")
+    runs = []
+    for family in ("whole", "tail", "portions", "mixed"):
+        steps, max_tokens = _family("P", reqs, family)
+        runs.append(run_trace_engine(folder, "float32", steps, max_tokens, PAGE_SIZES["P"]))
+    for other in runs[1:]:
+        worst = max(float(np.abs(other[k] - runs[0][k]).max()) for k in runs[0])
+        assert worst <= 2e-5, worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(models, dtype):
+    """bin/trace_run as a child process, the default page size, four slots, a mixed trace in which pages and slots are
+    used again."""
+    import tempfile
+    from pathlib import Path
+
+    folder, cfg, w = models["Q"]
+    reqs = _requests("Q")
+    steps, peak = mixed_trace(reqs, seed=9, max_live=4, max_tokens=round64(max(LENGTHS["Q"])) + 128)
+    with tempfile.TemporaryDirectory() as out:
+        cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", out,
+               "--max-tokens", str(peak)]
+        r = subprocess.run(cmd, input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
+        assert [l for l in r.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        outputs = {}
+        for s in steps:
+            wanted = sum(len(e["want"]) for e in s["entries"])
+            if wanted:
+                outputs[s["step"]] = np.fromfile(Path(out) / f"{s['step']}.f32", dtype="<f4").reshape(wanted, cfg["vocab"])
+    _compare(collect(steps, outputs), _expect(models, "Q"), "Q", dtype, "trace_run")
+
+
+# ---------------------------------------------------------------- generation through the scheduler
+
+
+def _plain_greedy(cfg, w, prompt, n_new):
+    toks = list(prompt)
+    for _ in range(n_new):
+        toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+@pytest.mark.parametrize("name, run_ahead, graphs", [("P", True, True), ("R", False, True), ("Q", True, False)])
+def test_greedy_generation_through_the_scheduler(models, name, run_ahead, graphs):
+    """Three prompts of unequal length taken in portions of five tokens while earlier ones already decode, decode
+    steps replayed from CUDA graphs and launched ahead of the host: the plain implementation's tokens."""
+    import quantinfer_b200 as q
+    from quantinfer_b200.engine import Engine
+
+    folder, cfg, w = models[name]
+    prompts = [random_tokens(n, cfg["vocab"], seed=n) for n in (13, 1, 27)]
+    eng = Engine.from_folder(folder, dtype="float32", page_size=PAGE_SIZES[name], max_tokens=512, max_requests=4, use_graphs=graphs)
+    model = q.Model.from_engine(eng, max_batch_tokens=16, chunk_size=5, run_ahead=run_ahead)
+    got = model.generate_batch(prompts, max_new_tokens=10, eos_token_id=None)
+    for p, g in zip(prompts, got):
+        assert g == _plain_greedy(cfg, w, p, 10), (name, len(p))
+    # again on the same engine: slots and pages of the first call are used again, state must start afresh
+    assert model.generate_batch(prompts[::-1], max_new_tokens=10, eos_token_id=None) == got[::-1]
+    assert model.generate_tokens(prompts[2], max_new_tokens=10, eos_token_id=None) == got[2]
+
+
+def test_command_line_generates_the_same_tokens(models):
+    folder, cfg, w = models["R"]
+    prompt = random_tokens(9, cfg["vocab"], seed=1)
+    r = subprocess.run([sys.executable, str(ROOT / "bin" / "quantinfer"), "generate", "--input", str(folder), "--tokens",
+                        ",".join(map(str, prompt)), "--max-new-tokens", "10", "--dtype", "float32", "--page-size", "8"],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("generated_tokens=")][0]
+    assert json.loads(line.split("=", 1)[1]) == _plain_greedy(cfg, w, prompt, 10)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_chunks_and_pages(models, dtype):
+    """Three tokens of prompt, then a hundred and fifty decoded one by one with given ids: every chunk's edge is
+    crossed by decoded tokens, pages fill and go back, the recurrent layers' state is carried through every step."""
+    folder, cfg, w = models["P"]
+    toks = random_tokens(153, cfg["vocab"], seed=8)
+    steps = tail_trace({"long": toks}, 150)
+    got = run_trace_engine(folder, dtype, steps, 192, PAGE_SIZES["P"])
+    _compare(got, plain_rows(cfg, w, {"long": toks}), "P", dtype, "long decode")
