@@ -195,6 +195,99 @@ moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restri
     }
 }
 
+// The same product on the tensor cores for bfloat16 operands and results (mma.sync m16n8k16, 32-bit sums, K a
+// multiple of 8): a CTA of four warps takes one row tile (up to 32 sorted rows of one expert) and 64 output columns;
+// the next 32 of K are requested into registers while the current ones are multiplied.
+constexpr int MN = 64, MK = 32, MPAD = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const qi::bf16* __restrict__ x, const qi::bf16* __restrict__ w, qi::bf16* __restrict__ y,
+                    const int* __restrict__ tiles, const int* __restrict__ order, int top, int gather, int N, int K,
+                    long long ldx, long long ldy) {
+    __shared__ __align__(16) qi::bf16 As[BM][MK + MPAD];
+    __shared__ __align__(16) qi::bf16 Bs[MN][MK + MPAD];
+    __shared__ int src_row[BM];
+    qi::pdl_wait();
+    const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
+    if (expert < 0) return;
+    const qi::bf16* we = w + (size_t)expert * N * K;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n0 = blockIdx.x * MN;
+    if (tid < BM) src_row[tid] = tid < rows ? (gather ? order[row0 + tid] / top : row0 + tid) : -1;
+    __syncthreads();
+    const int ar = tid >> 2, ac = (tid & 3) * 8;           // this thread's 16-byte piece of the A tile (32 x 32)
+    const qi::bf16* a_src = src_row[ar] >= 0 ? x + (size_t)src_row[ar] * ldx + ac : nullptr;
+    const qi::bf16* b_src[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                          // and its two pieces of the B tile (64 x 32)
+        const int br = (tid >> 2) + 32 * i;
+        b_src[i] = n0 + br < N ? we + (size_t)(n0 + br) * K + ac : nullptr;
+    }
+    auto fetch = [&](int k0, uint4& a, uint4 (&b)[2]) {
+        const bool in = k0 + ac < K;
+        a = (in && a_src) ? *reinterpret_cast<const uint4*>(a_src + k0) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) b[i] = (in && b_src[i]) ? *reinterpret_cast<const uint4*>(b_src[i] + k0) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    float acc[2][2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+    uint4 a_reg, b_reg[2];
+    fetch(0, a_reg, b_reg);
+    for (int k0 = 0; k0 < K; k0 += MK) {
+        __syncthreads();
+        *reinterpret_cast<uint4*>(&As[ar][ac]) = a_reg;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) *reinterpret_cast<uint4*>(&Bs[(tid >> 2) + 32 * i][ac]) = b_reg[i];
+        __syncthreads();
+        if (k0 + MK < K) fetch(k0 + MK, a_reg, b_reg);
+#pragma unroll
+        for (int kk = 0; kk < MK / 16; ++kk) {
+            uint32_t a[2][4], b[2][2];
+            const int c = kk * 16 + (lane & 3) * 2;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = i * 16 + (lane >> 2);
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][c]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][c + 8]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][c + 8]);
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const int nn = warp * 16 + j * 8 + (lane >> 2);
+                b[j][0] = *reinterpret_cast<const uint32_t*>(&Bs[nn][c]);
+                b[j][1] = *reinterpret_cast<const uint32_t*>(&Bs[nn][c + 8]);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) mma_bf16_16816(acc[i][j], a[i][0], a[i][1], a[i][2], a[i][3], b[j][0], b[j][1]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const int n = n0 + warp * 16 + j * 8 + (lane & 3) * 2;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int m = i * 16 + (lane >> 2) + 8 * half;
+                if (m >= rows) continue;
+                qi::bf16* dst = y + (size_t)(row0 + m) * ldy + n;
+                if (n < N) dst[0] = __float2bfloat16_rn(acc[i][j][2 * half]);
+                if (n + 1 < N) dst[1] = __float2bfloat16_rn(acc[i][j][2 * half + 1]);
+            }
+        }
+}
+
 template <typename TY, typename TO>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
@@ -246,6 +339,11 @@ extern "C" int qi_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtyp
     QI_REQUIRE(ldx >= K && ldy >= N, "moe_gemm: a leading dimension is smaller than its row");
     QI_REQUIRE(max_tiles <= 65535, "moe_gemm: %d row tiles are too many for one launch", max_tiles);
     if (max_tiles == 0) return 0;
+    if (x_dtype == qi::kBF16 && w_dtype == qi::kBF16 && y_dtype == qi::kBF16 && K % 8 == 0 && ldx % 8 == 0) {
+        qi::launch(moe_gemm_mma_kernel, dim3((N + MN - 1) / MN, max_tiles), dim3(128), 0, stream, (const qi::bf16*)x,
+                   (const qi::bf16*)w, (qi::bf16*)y, tiles, order, top, gather, N, K, ldx, ldy);
+        return qi::check_launch("moe_gemm_mma");
+    }
     const dim3 grid((N + BN - 1) / BN, max_tiles), block(256);
     QI_DISPATCH_DTYPE(x_dtype, TX, {
         QI_DISPATCH_DTYPE(w_dtype, TW, {

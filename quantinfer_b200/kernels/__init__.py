@@ -1210,9 +1210,38 @@ def moe_combine(y, place, weights, shared, out) -> None:
           _code(out), n, top, width, _stream())
 
 
+def gated_attention_mma_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
+    """Whether the tensor-core kernel for separate key and value sizes takes this geometry (bfloat16 only)."""
+    return bool(library().qi_gated_attention_mma_supported(nq, nkv, d, dv))
+
+
 def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv, scale: float, window: int, chunk: int, gate,
-                    status) -> None:
+                    status, impl: str | None = None) -> None:
     """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
-    kernel that fits the step."""
-    attention_generic(q, out, k_pages, v_pages, block_table, batch.positions, batch.token_req, nq, nkv, d, scale, window,
-                      status, chunk=chunk, gate=gate)
+    kernel that fits: "mma" (bfloat16, head sizes that are multiples of 8 up to 128: flash form on the tensor
+    cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes)."""
+    if impl is None:
+        impl = "mma" if q.dtype == torch.bfloat16 and gated_attention_mma_supported(nq, nkv, d, dv) and (
+            gate is None or gate.stride(0) % 2 == 0) else "generic"
+    if impl == "generic":
+        return attention_generic(q, out, k_pages, v_pages, block_table, batch.positions, batch.token_req, nq, nkv, d, scale,
+                                 window, status, chunk=chunk, gate=gate)
+    _req(q, "q", torch.bfloat16, 2)
+    _req(out, "out", torch.bfloat16, 2)
+    _req(k_pages, "k_pages", torch.bfloat16, 4)
+    _req(v_pages, "v_pages", torch.bfloat16, 4)
+    _req(block_table, "block_table", torch.int32, 2)
+    n = q.shape[0]
+    if q.shape[1] != nq * d or tuple(out.shape) != (n, nq * dv):
+        raise KernelError(f"gated_attention: q {tuple(q.shape)} / out {tuple(out.shape)} do not match {nq} heads of {d} / {dv}")
+    if tuple(k_pages.shape[1:]) != (nkv, k_pages.shape[2], d) or tuple(v_pages.shape) != (k_pages.shape[0], nkv, k_pages.shape[2], dv):
+        raise KernelError(f"gated_attention: pages {tuple(k_pages.shape)} / {tuple(v_pages.shape)} do not fit")
+    ldg = 0
+    if gate is not None:
+        if not gate.is_cuda or gate.dtype != q.dtype or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
+            raise KernelError("gated_attention: the gate must be [n, nq dv] in q's type with contiguous rows")
+        ldg = gate.stride(0)
+    _call("attention", "gated_attention_mma", library().qi_gated_attention_mma, _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages),
+          _ptr(block_table), block_table.shape[1], k_pages.shape[2], k_pages.shape[0], _ptr(batch.q_start), _ptr(batch.start_pos),
+          batch.n_requests, n, nq, nkv, d, dv, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate), C.c_longlong(ldg),
+          _ptr(status), _stream())

@@ -142,6 +142,60 @@ def test_router_choice_and_weights(E, top):
     assert sorted(covered) == list(range(n * top))
 
 
+@pytest.mark.parametrize("impl", ["mma", "generic"])
+@pytest.mark.parametrize("d, dv, H, G, chunk, window, page", [(96, 96, 4, 2, 64, 0, 64), (16, 32, 4, 1, 20, 0, 8), (128, 64, 2, 2, 0, 0, 16),
+                                                             (40, 8, 6, 3, 100, 37, 32), (64, 128, 8, 2, 7, 0, 64), (24, 24, 1, 1, 0, 50, 8)])
+def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, chunk, window, page):
+    """Decode tokens in front of prompt portions in one launch, contexts of unequal length on pages handed out in
+    random order, NaN in every page that lies wholly before what a request's rows may see (such pages go back to
+    the pool while the request runs), a gate, keys and values of unequal size."""
+    from types import SimpleNamespace
+
+    from quantinfer_b200 import kernels as k
+
+    torch.manual_seed(d + dv)
+    starts, lens = [130, 5, 0, 63, 200], [1, 1, 70, 129, 9]
+    B, max_blocks = len(lens), 6 * 64 // page
+    n_pages = B * max_blocks
+    perm = torch.randperm(n_pages)
+    kp = torch.randn(n_pages, G, page, d).to(torch.bfloat16)
+    vp = torch.randn(n_pages, G, page, dv).to(torch.bfloat16)
+    table = perm.view(B, max_blocks).to(torch.int32)
+    n = sum(lens)
+    q = (torch.randn(n, H, d) * 1.5).to(torch.bfloat16)
+    gate = torch.randn(n, H * dv + 6).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(d)
+    ref = torch.zeros(n, H, dv, dtype=torch.float64)
+    lo_of = lambda p: max(p - window + 1 if window else 0, p // chunk * chunk if chunk else 0, 0)
+    t = 0
+    for e in range(B):
+        keys = torch.stack([kp[table[e, j // page], :, j % page] for j in range(starts[e] + lens[e])]).double()
+        vals = torch.stack([vp[table[e, j // page], :, j % page] for j in range(starts[e] + lens[e])]).double()
+        for i in range(lens[e]):
+            p = starts[e] + i
+            lo = lo_of(p)
+            for h in range(H):
+                g = h // (H // G)
+                w = torch.softmax((keys[lo:p + 1, g] @ q[t, h].double()) * scale, dim=0)
+                ref[t, h] = (w[:, None] * vals[lo:p + 1, g]).sum(dim=0) * torch.sigmoid(gate[t, h * dv:(h + 1) * dv].double())
+            t += 1
+        for b in range(lo_of(starts[e]) // page):          # pages no row of this entry sees
+            kp[table[e, b]] = float("nan")
+            vp[table[e, b]] = float("nan")
+    I = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    batch = SimpleNamespace(q_start=I([0] + np.cumsum(lens).tolist()), start_pos=I(starts), n_requests=B,
+                            positions=I([s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]),
+                            token_req=I([e for e, ln in enumerate(lens) for _ in range(ln)]))
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((n, H * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
+    gd = gate.to(DEV)
+    k.gated_attention(q.view(n, H * d).to(DEV), out, kp.to(DEV), vp.to(DEV), table.to(DEV), batch, H, G, d, dv, scale, window, chunk,
+                      gd[:, :H * dv], status, impl=impl)
+    assert int(status.item()) == 0
+    err = (out.cpu().double().view(n, H, dv) - ref).abs()
+    assert float(err.max()) < 0.03, (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+
+
 # ---------------------------------------------------------------- one mixer or feed-forward alone, in an engine of one layer
 
 
