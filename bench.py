@@ -156,8 +156,55 @@ def latent_arithmetic(config, spec):
     return a
 
 
+def kiruvik_arithmetic(config, spec):
+    """The same for a model of the Kiruvik design: per layer the mixer's projections (attention: q, k, v, gate, out;
+    state-space: in, out), the feed-forward a token runs (dense: three matrices; mixture: router, `top` experts, the
+    shared expert), attention over the keys of the query's chunk, the recurrence's multiply-adds. `weight_bytes` counts
+    what a decode step of `batch` tokens reads of a mixture: the experts it can be expected to touch."""
+    from quantinfer_b200.config.kiruvik import KiruvikAttention, KiruvikDense, KiruvikMoE
+
+    H, V = spec.hidden_size, spec.vocab_size
+    order = [i for i, _ in config.run_order()]
+    active = stored = touched = kv = scan_flops = state_bytes = 0
+    chunks, batch = [], COMPARE_BATCH
+    for i in order:
+        layer = config.layers[i]
+        m, f = layer.mixer, layer.mlp
+        if isinstance(m, KiruvikAttention):
+            mix = H * ((m.heads + m.kv_heads) * m.dim + m.kv_heads * m.vdim + m.heads * m.vdim) + m.heads * m.vdim * H
+            kv += 2 * m.kv_heads * (m.dim + m.vdim)
+            chunks.append((m.heads, m.dim, m.vdim, m.kv_heads, m.chunk))
+        else:
+            inner = m.heads * m.vdim
+            mix = H * (2 * inner + 2 * m.groups * m.state + m.heads) + inner * H
+            scan_flops += 6.0 * inner * m.state
+            state_bytes += 2 * 4 * inner * m.state
+        active += mix; stored += mix; touched += mix
+        if isinstance(f, KiruvikDense):
+            active += 3 * H * f.ff; stored += 3 * H * f.ff; touched += 3 * H * f.ff
+        elif isinstance(f, KiruvikMoE):
+            one = 3 * H * f.ff
+            sh = 3 * H * f.shared_ff if f.shared_ff else 0
+            active += f.top * one + sh + f.experts * H
+            stored += f.experts * one + sh + f.experts * H
+            touched += f.experts * (1.0 - (1.0 - f.top / f.experts) ** batch) * one + sh + f.experts * H
+    if config.loop is not None:
+        active += 2 * H * H * config.loop[2]; stored += 2 * H * H; touched += 2 * H * H
+    a = dict(L=len(order), H=H, V=V, layer_params=active / len(order), stored_params=stored)
+    a["weight_bytes"] = 2 * (touched + V * H)
+    a["kv_bytes_per_token"] = 0
+    a["kv_bytes"] = lambda ctx: sum(2 * g * (d + dv) * (min(ctx, ctx % c + 1) if c else ctx) for _, d, dv, g, c in chunks)
+    a["state_bytes"] = state_bytes
+    a["gemm_flops"] = lambda T, rows_=1: 2.0 * T * active + 2.0 * H * V * rows_
+    a["attn_flops"] = lambda T: sum(2.0 * h * (d + dv) * sum((t % c if c else t) + 1 for t in range(T)) for h, d, dv, _, c in chunks)
+    a["scan_flops"] = lambda T: scan_flops * T
+    return a
+
+
 def model_arithmetic(config, spec):
     """Parameter counts, bytes and flops of the configuration (every matrix bf16)."""
+    if type(config).__name__ == "KiruvikConfig":
+        return kiruvik_arithmetic(config, spec)
     if hasattr(config, "layers"):
         return latent_arithmetic(config, spec)
     L, H, I, V = len(spec.layers), spec.hidden_size, config.intermediate_size, spec.vocab_size
@@ -440,6 +487,100 @@ def compare_entries(size):
             dict(common, config=dense, name=f"Qwen3 layers of width {size}"))
 
 
+# ---- the Kiruvik design beside dense layers of equal width ------------------------------------------------------
+# (width, heads / kv heads of 128, dense feed-forward, experts x their feed-forward, shared expert, state-space heads of 64
+# with a state of 128 rows): four layers, attention + dense, state-space + mixture, attention + mixture, state-space + dense
+KIRUVIK_SIZES = {
+    "2048": dict(width=2048, heads=16, kv=4, ff=8192, experts=16, eff=2048, sff=2048, sheads=64),
+    "4096": dict(width=4096, heads=32, kv=8, ff=12288, experts=32, eff=2048, sff=4096, sheads=128),
+}
+KIRUVIK_CHUNK, KIRUVIK_TOP = 1024, 4
+
+
+def kiruvik_entries(size):
+    z = KIRUVIK_SIZES[size]
+    att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}}
+    rec = {"heads": z["sheads"], "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    mix = {"kind": "moe", "router": {"experts": z["experts"], "top": KIRUVIK_TOP, "scale": 2.5},
+           "expert": {"ff": z["eff"], "limit": 7.0}, "shared": {"ff": z["sff"], "limit": 7.0}}
+    den = {"kind": "dense", "ff": z["ff"]}
+    layers = [{"type": "attention", "mixer": att, "mlp": den}, {"type": "mamba2", "mixer": rec, "mlp": mix},
+              {"type": "attention", "mixer": att, "mlp": mix}, {"type": "mamba2", "mixer": rec, "mlp": den}]
+    new = dict(architecture="Kiruvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, residual_mult=0.5, layers=layers)
+    dense = dict(_COMMON, vocab_size=COMPARE_VOCAB, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=COMPARE_LAYERS,
+                 num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=128)
+    common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())
+    return (dict(common, config=new, name=f"Kiruvik layers of width {size}"), dict(common, config=dense, name=f"Qwen3 layers of width {size}"))
+
+
+def compare_kiruvik(args):
+    """Prefill and decode throughput of four Kiruvik layers (attention and state-space mixers, dense and routed
+    feed-forwards) beside four dense GQA layers of the same width, heads and vocabulary, and each kernel class of both
+    alone (the others left out of the step) with its share of the roofline."""
+    import gc
+
+    import torch
+
+    from quantinfer_b200 import kernels
+
+    hbm, sustained, burst, src = peaks()
+    out = {"compare": "Kiruvik layers beside dense GQA (Qwen3) layers of equal width", "layers": COMPARE_LAYERS, "vocab": COMPARE_VOCAB,
+           "prompt": COMPARE_PROMPT, "decode_batch": COMPARE_BATCH, "chunk": KIRUVIK_CHUNK, "peaks": src, "sizes": {}}
+    every = ("gemm", "attention", "norm", "rope", "scan", "other")
+    for size in (args.compare_sizes.split(",") if args.compare_sizes else list(KIRUVIK_SIZES)):
+        rows = {}
+        for entry in kiruvik_entries(size):
+            args.batch = COMPARE_BATCH
+            bench = Bench(args, entry)
+            a, T = bench.arith, bench.prompt_len
+            head = bench.decode_rate(COMPARE_BATCH, args.steps, args.warmup)
+            pre_ms = bench.prefill_ms()
+            ctx = int(head["ctx_mid"])
+            kv_bytes = COMPARE_BATCH * (a["kv_bytes"](ctx) if "kv_bytes" in a else ctx * a["kv_bytes_per_token"])
+            state_bytes = COMPARE_BATCH * a.get("state_bytes", 0)
+            flops = a["gemm_flops"](T) + a["attn_flops"](T) + (a["scan_flops"](T) if "scan_flops" in a else 0.0)
+            step_bytes = a["weight_bytes"] + kv_bytes + state_bytes
+            print(f"[compare] {entry['name']}: decode {head['ms']:.3f} ms a step, prefill {pre_ms:.3f} ms", file=sys.stderr, flush=True)
+            row = {"decode_tokens_per_s": round(head["rate"], 1), "decode_ms": round(head["ms"], 4),
+                   "decode_launches_per_step": head["launches"] // args.steps,
+                   "decode_frac_hbm": round(step_bytes / (head["ms"] * 1e-3) / 1e9 / hbm, 3),
+                   "prefill_tokens_per_s": round(T / pre_ms * 1e3, 1), "prefill_ms": round(pre_ms, 3),
+                   "prefill_frac_burst": round(flops / (pre_ms * 1e-3) / 1e12 / burst, 3), "weight_gb": round(a["weight_bytes"] / 1e9, 3), "classes": {}}
+            work = {"gemm": (a["weight_bytes"], a["gemm_flops"](T)), "attention": (kv_bytes, a["attn_flops"](T))}
+            if "scan_flops" in a:
+                work["scan"] = (state_bytes, a["scan_flops"](T))
+
+            def timed(knocked):
+                kernels.knock_out = frozenset(knocked)
+                bench.engine._graphs.clear()
+                try:
+                    return bench.decode_rate(COMPARE_BATCH, 16, 3)["ms"], bench.prefill_ms(runs=3, warm=1)
+                finally:
+                    kernels.knock_out = frozenset()
+                    bench.engine._graphs.clear()
+
+            rest = [head["ms"], pre_ms]
+            for cls in work:
+                d_alone, _ = timed([c for c in every if c != cls])
+                _, p_without = timed([cls])
+                c = {"decode_alone_ms": round(d_alone, 4), "prefill_left_out_ms": round(pre_ms - p_without, 4)}
+                if d_alone > 0 and pre_ms > p_without:
+                    c["decode_frac_hbm"] = round(work[cls][0] / (d_alone * 1e-3) / 1e9 / hbm, 4)
+                    c["prefill_frac_burst"] = round(work[cls][1] / ((pre_ms - p_without) * 1e-3) / 1e12 / burst, 4)
+                rest[0] -= d_alone
+                rest[1] -= pre_ms - p_without
+                row["classes"][cls] = c
+                print(f"[compare] {entry['name']} {cls}: {c}", file=sys.stderr, flush=True)
+            row["classes"]["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
+            rows[entry["name"]] = row
+            del bench
+            gc.collect()
+            torch.cuda.empty_cache()
+        out["sizes"][size] = rows
+    return out
+
+
 def compare_designs(args):
     """Prefill and decode throughput of latent-attention layers and of dense GQA layers of the same width, head
     count, query/key size, depth and vocabulary, and every kernel class of each alone with its share of the roofline."""
@@ -702,8 +843,9 @@ def main() -> int:
                     help="run one part only (for profiler captures of a small case)")
     ap.add_argument("--timeline", action="store_true",
                     help="build the kernels with their time stamps and print where a decode step's time goes, kernel by kernel")
-    ap.add_argument("--compare", action="store_true",
-                    help="instead of the headline workload: latent-attention layers beside dense GQA layers of equal sizes")
+    ap.add_argument("--compare", nargs="?", const="bebuvik", default=None, choices=["bebuvik", "kiruvik"],
+                    help="instead of the headline workload: layers of another design (default: the latent-attention design) "
+                         "beside dense GQA layers of equal sizes")
     ap.add_argument("--compare-sizes", default=None, help="widths to compare, with commas between them (default: all)")
     args = ap.parse_args()
     if args.timeline:
@@ -730,7 +872,7 @@ def main() -> int:
     torch.cuda.set_device(0)
     if args.compare:
         args.skip_points = args.skip_classes = True
-        print(json.dumps(compare_designs(args)))
+        print(json.dumps(compare_kiruvik(args) if args.compare == "kiruvik" else compare_designs(args)))
         return 0
     if args.only == "mixed":
         print(json.dumps({"only": "mixed", "mixed": mixed_workload(args, entry)}))

@@ -65,6 +65,7 @@ moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ cor
             const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
+        if (best_e >= E) best_e = k % E;      // scores that are not numbers: any valid expert, so that what follows stays in range
         float sc = 0.f;
 #pragma unroll
         for (int i = 0; i < kMaxPerLane; ++i)
@@ -134,18 +135,20 @@ constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TX* __restrict__ x, const TW* __restrict__ w, TY* __restrict__ y, const int* __restrict__ tiles,
-                const int* __restrict__ order, int top, int gather, int N, int K, long long ldx, long long ldy) {
+                const int* __restrict__ order, int top, int gather, int N, int K, long long ldx, long long ldy, int n_src,
+                int n_rows, int n_experts) {
     __shared__ float xs[BK][BM + 4];
     __shared__ float ws[BK][BN + 4];
     __shared__ int src_row[BM];
     qi::pdl_wait();
     const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
-    if (expert < 0) return;
+    if (expert < 0 || expert >= n_experts || row0 < 0 || rows < 0 || rows > BM || row0 + rows > n_rows) return;
     const TW* we = w + (size_t)expert * N * K;
     const int tid = threadIdx.x;
     const int tx = tid % 16, ty = tid / 16;  // tx over N (16 x TN = 64), ty over M (16 x TM = 32)
     const int n0 = blockIdx.x * BN;
     if (tid < BM) src_row[tid] = tid < rows ? (gather ? order[row0 + tid] / top : row0 + tid) : -1;
+    if (tid < BM && (src_row[tid] < 0 || src_row[tid] >= n_src)) src_row[tid] = -1;
     __syncthreads();
 
     float acc[TM][TN];
@@ -208,17 +211,18 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
 __global__ void __launch_bounds__(128)
 moe_gemm_mma_kernel(const qi::bf16* __restrict__ x, const qi::bf16* __restrict__ w, qi::bf16* __restrict__ y,
                     const int* __restrict__ tiles, const int* __restrict__ order, int top, int gather, int N, int K,
-                    long long ldx, long long ldy) {
+                    long long ldx, long long ldy, int n_src, int n_rows, int n_experts) {
     __shared__ __align__(16) qi::bf16 As[BM][MK + MPAD];
     __shared__ __align__(16) qi::bf16 Bs[MN][MK + MPAD];
     __shared__ int src_row[BM];
     qi::pdl_wait();
     const int expert = tiles[3 * blockIdx.y], row0 = tiles[3 * blockIdx.y + 1], rows = tiles[3 * blockIdx.y + 2];
-    if (expert < 0) return;
+    if (expert < 0 || expert >= n_experts || row0 < 0 || rows < 0 || rows > BM || row0 + rows > n_rows) return;
     const qi::bf16* we = w + (size_t)expert * N * K;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * MN;
     if (tid < BM) src_row[tid] = tid < rows ? (gather ? order[row0 + tid] / top : row0 + tid) : -1;
+    if (tid < BM && (src_row[tid] < 0 || src_row[tid] >= n_src)) src_row[tid] = -1;
     __syncthreads();
     const int ar = tid >> 2, ac = (tid & 3) * 8;           // this thread's 16-byte piece of the A tile (32 x 32)
     const qi::bf16* a_src = src_row[ar] >= 0 ? x + (size_t)src_row[ar] * ldx + ac : nullptr;
@@ -298,14 +302,63 @@ moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ place, cons
         const size_t t = idx / width;
         const int c = (int)(idx % width);
         float acc = 0.f;
-        for (int k = 0; k < top; ++k)
-            acc = fmaf(weights[t * top + k], qi::to_f32<TY>(y[(size_t)place[t * top + k] * width + c]), acc);
+        for (int k = 0; k < top; ++k) {
+            const int pl = place[t * top + k];
+            if (pl >= 0 && pl < n * top) acc = fmaf(weights[t * top + k], qi::to_f32<TY>(y[(size_t)pl * width + c]), acc);
+        }
         if (shared) acc += qi::to_f32<TY>(shared[idx]);
         out[idx] = qi::from_f32<TO>(acc);
     }
 }
 
+// out[i] = x[order[i] / top]: the tokens' rows in the experts' order.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ order, int top, T* __restrict__ out, int n_pairs, int n_src, int K) {
+    qi::pdl_wait();
+    const size_t total = (size_t)n_pairs * K;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t i = idx / K;
+        const int src = order[i] / top;
+        out[idx] = (src >= 0 && src < n_src) ? x[(size_t)src * K + idx % K] : qi::from_f32<T>(0.f);
+    }
+}
+
 }  // namespace
+
+extern "C" int qi_moe_gather(const void* x, int dtype, const int* order, int top, void* out, int n_pairs, int n_src, int K,
+                             cudaStream_t stream) {
+    QI_REQUIRE(n_pairs >= 0 && n_src >= 0 && K > 0 && top > 0, "moe_gather: bad sizes");
+    if (n_pairs == 0) return 0;
+    size_t blocks = ((size_t)n_pairs * K + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    QI_DISPATCH_DTYPE(dtype, T, {
+        qi::launch(moe_gather_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, (const T*)x, order, top, (T*)out, n_pairs, n_src, K);
+    });
+    return qi::check_launch("moe_gather");
+}
+
+extern "C" int qi_gemm_bf16_plan(int M, int N, int K, int allow_split, int* swap, int* bn, int* splits);
+extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dtype, int M, int N, int K, int swap, int bn,
+                            int splits, int epilogue, void* workspace, int* status, cudaStream_t stream);
+
+// Every expert's rows through the dense tensor-core product, one launch an expert: x [pairs, K] in the experts' order,
+// w [E, N, K], y [pairs, N], all bfloat16; bounds (HOST memory) [E + 1]: expert e owns rows bounds[e] .. bounds[e + 1] - 1.
+extern "C" int qi_moe_gemm_by_expert(const void* x, const void* w, void* y, const int* bounds, int E, int N, int K, int* status,
+                                     cudaStream_t stream) {
+    QI_REQUIRE(E > 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0, "moe_gemm_by_expert: bad sizes E=%d N=%d K=%d", E, N, K);
+    for (int e = 0; e < E; ++e) {
+        const int a = bounds[e], M = bounds[e + 1] - a;
+        QI_REQUIRE(a >= 0 && M >= 0, "moe_gemm_by_expert: the experts' bounds do not ascend");
+        if (M == 0) continue;
+        int swap, bn, splits;
+        qi_gemm_bf16_plan(M, N, K, 0, &swap, &bn, &splits);
+        const int rc = qi_gemm_bf16((const qi::bf16*)x + (size_t)a * K, (const qi::bf16*)w + (size_t)e * N * K,
+                                    (qi::bf16*)y + (size_t)a * N, qi::kBF16, M, N, K, swap, bn, 1, 0, nullptr, status, stream);
+        if (rc) return rc;
+    }
+    return 0;
+}
 
 extern "C" int qi_moe_tile_rows() { return BM; }
 
@@ -332,16 +385,17 @@ extern "C" int qi_moe_group(const int* ids, int n_pairs, int E, int tile, int ma
 }
 
 // x rows of K (ldx apart); w [E, N, K]; y [n_rows, N] (ldy apart); tiles as moe_group wrote them with tile = qi_moe_tile_rows().
+// n_src: rows of x; n_rows: rows of y (the number of (token, choice) pairs); E: experts. Tiles or source rows outside these are skipped.
 extern "C" int qi_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtype, void* y, int y_dtype, const int* tiles,
                            int max_tiles, const int* order, int top, int gather, int N, int K, long long ldx, long long ldy,
-                           cudaStream_t stream) {
+                           int n_src, int n_rows, int E, cudaStream_t stream) {
     QI_REQUIRE(max_tiles >= 0 && N > 0 && K > 0 && top > 0, "moe_gemm: bad sizes");
     QI_REQUIRE(ldx >= K && ldy >= N, "moe_gemm: a leading dimension is smaller than its row");
     QI_REQUIRE(max_tiles <= 65535, "moe_gemm: %d row tiles are too many for one launch", max_tiles);
     if (max_tiles == 0) return 0;
     if (x_dtype == qi::kBF16 && w_dtype == qi::kBF16 && y_dtype == qi::kBF16 && K % 8 == 0 && ldx % 8 == 0) {
         qi::launch(moe_gemm_mma_kernel, dim3((N + MN - 1) / MN, max_tiles), dim3(128), 0, stream, (const qi::bf16*)x,
-                   (const qi::bf16*)w, (qi::bf16*)y, tiles, order, top, gather, N, K, ldx, ldy);
+                   (const qi::bf16*)w, (qi::bf16*)y, tiles, order, top, gather, N, K, ldx, ldy, n_src, n_rows, E);
         return qi::check_launch("moe_gemm_mma");
     }
     const dim3 grid((N + BN - 1) / BN, max_tiles), block(256);
@@ -349,7 +403,7 @@ extern "C" int qi_moe_gemm(const void* x, int x_dtype, const void* w, int w_dtyp
         QI_DISPATCH_DTYPE(w_dtype, TW, {
             QI_DISPATCH_DTYPE(y_dtype, TY, {
                 qi::launch(moe_gemm_kernel<TX, TW, TY>, grid, block, 0, stream, (const TX*)x, (const TW*)w, (TY*)y, tiles, order, top,
-                           gather, N, K, ldx, ldy);
+                           gather, N, K, ldx, ldy, n_src, n_rows, E);
             });
         });
     });

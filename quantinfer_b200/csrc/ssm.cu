@@ -12,7 +12,9 @@
 //
 // ssm_scan: one warp walks the tokens of one step entry for `kCols` channels of one head: lane l keeps
 // S[n, p] for n = l, l + 32, ... in registers, so a token costs each lane a few multiply-adds and one
-// warp sum per channel; the next token's operands are requested before the current one is worked on.
+// warp sum per channel. The four warps of a block share a head: B, C, x, the step sizes and decays of
+// sixteen tokens at a time are brought into shared memory together (one round of loads for sixteen
+// steps of the recurrence), and the results leave in rows.
 // The state is read once at the entry's first token (zeros at position 0, whatever the slot holds) and
 // written once after its last, so one launch serves prompts, portions and single decode tokens alike.
 // State layout per slot: [heads, P, N] (N fastest, so a warp's loads are contiguous).
@@ -25,6 +27,7 @@ namespace {
 
 constexpr int kCols = 4;       // channels a warp
 constexpr int kWarps = 4;      // warps a block
+constexpr int kBatch = 16;     // tokens whose operands are staged in shared memory at a time
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
@@ -34,12 +37,21 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                 float* __restrict__ state, long long state_stride, float* __restrict__ y,
                 const int* __restrict__ q_start, const int* __restrict__ start_pos, const int* __restrict__ slot_ids,
-                int heads, int groups, int P, int N) {
+                int heads, int groups, int P, int N, int write_state) {
+    // a batch of kBatch tokens' operands, 32-bit: B and C [kBatch][N], x and the results [kBatch][block's columns], dt, decay
+    extern __shared__ float sm[];
+    constexpr int kBlockCols = kWarps * kCols;
+    float* Bs = sm;
+    float* Cs = Bs + kBatch * N;
+    float* xs = Cs + kBatch * N;
+    float* ys = xs + kBatch * kBlockCols;
+    float* dts = ys + kBatch * kBlockCols;
+    float* decs = dts + kBatch;
     qi::pdl_wait();
     const int h = blockIdx.x, e = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int p0 = (blockIdx.z * kWarps + warp) * kCols;
-    if (p0 >= P) return;
+    const int pb = blockIdx.z * kBlockCols;          // the block's first channel of the head
+    const int p0 = pb + warp * kCols;                // the warp's
     const int g = h / (heads / groups);
     const int inner = heads * P;
     const int t0 = q_start[e], t1 = q_start[e + 1];
@@ -56,50 +68,72 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
             S[c][r] = (!fresh && n < N && p0 + c < P) ? st[(size_t)c * N + n] : 0.f;
         }
 
-    const size_t xoff = (size_t)h * P + p0, boff = (size_t)inner + (size_t)g * N, coff = (size_t)inner + (size_t)groups * N + (size_t)g * N;
-    float Bn[R], Cn[R], xn[kCols], rn;
-    auto fetch = [&](int t) {
-        const T* row = xbc + (size_t)t * ldx;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int n = lane + 32 * r;
-            Bn[r] = n < N ? qi::to_f32<T>(row[boff + n]) : 0.f;
-            Cn[r] = n < N ? qi::to_f32<T>(row[coff + n]) : 0.f;
+    const size_t xoff = (size_t)h * P + pb, boff = (size_t)inner + (size_t)g * N, coff = (size_t)inner + (size_t)groups * N + (size_t)g * N;
+    for (int tb = t0; tb < t1; tb += kBatch) {
+        const int nb = min(kBatch, t1 - tb);
+        __syncthreads();                              // the batch before is consumed and written
+        for (int idx = threadIdx.x; idx < nb * N; idx += blockDim.x) {
+            const int i = idx / N, n = idx % N;
+            const T* row = xbc + (size_t)(tb + i) * ldx;
+            Bs[i * N + n] = qi::to_f32<T>(row[boff + n]);
+            Cs[i * N + n] = qi::to_f32<T>(row[coff + n]);
         }
-#pragma unroll
-        for (int c = 0; c < kCols; ++c) xn[c] = p0 + c < P ? qi::to_f32<T>(row[xoff + c]) : 0.f;
-        rn = qi::to_f32<T>(raw_dt[(size_t)t * lddt + h]);
-    };
-    if (t0 < t1) fetch(t0);
-    for (int t = t0; t < t1; ++t) {
-        float B[R], C[R], x[kCols];
-#pragma unroll
-        for (int r = 0; r < R; ++r) { B[r] = Bn[r]; C[r] = Cn[r]; }
-#pragma unroll
-        for (int c = 0; c < kCols; ++c) x[c] = xn[c];
-        const float raw = rn;
-        if (t + 1 < t1) fetch(t + 1);
-        const float dt = softplus_f(raw + bias);
-        const float a = expf(A * dt);
-        float out[kCols];
-#pragma unroll
-        for (int c = 0; c < kCols; ++c) {
-            const float dx = dt * x[c];
-            float part = 0.f;
+        for (int idx = threadIdx.x; idx < nb * kBlockCols; idx += blockDim.x) {
+            const int i = idx / kBlockCols, c = idx % kBlockCols;
+            xs[idx] = pb + c < P ? qi::to_f32<T>(xbc[(size_t)(tb + i) * ldx + xoff + c]) : 0.f;
+        }
+        if ((int)threadIdx.x < nb) {
+            const float dt = softplus_f(qi::to_f32<T>(raw_dt[(size_t)(tb + threadIdx.x) * lddt + h]) + bias);
+            dts[threadIdx.x] = dt;
+            decs[threadIdx.x] = expf(A * dt);
+        }
+        __syncthreads();
+        for (int i = 0; i < nb; ++i) {
+            const float dt = dts[i], a = decs[i];
+            float B[R], C[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                S[c][r] = fmaf(a, S[c][r], dx * B[r]);
-                part = fmaf(S[c][r], C[r], part);
+                const int n = lane + 32 * r;
+                B[r] = n < N ? Bs[i * N + n] : 0.f;
+                C[r] = n < N ? Cs[i * N + n] : 0.f;
             }
-            out[c] = qi::warp_sum(part) + D * x[c];
-        }
-        if (lane < kCols && p0 + lane < P) {
-            float v = out[0];
+            float part[kCols];
 #pragma unroll
-            for (int c = 1; c < kCols; ++c) if (lane == c) v = out[c];
-            y[(size_t)t * inner + xoff + lane] = v;
+            for (int c = 0; c < kCols; ++c) {
+                const float dx = dt * xs[i * kBlockCols + warp * kCols + c];
+                part[c] = 0.f;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    S[c][r] = fmaf(a, S[c][r], dx * B[r]);
+                    part[c] = fmaf(S[c][r], C[r], part[c]);
+                }
+            }
+            if (!y) continue;          // a pass that is after the end state only
+            // the four channels' sums over the warp in six exchanges: halves trade channels, then quarters, then the
+            // eight lanes that are left add up; lanes 0, 8, 16 and 24 end up with channels 0, 1, 2 and 3
+            static_assert(kCols == 4, "the exchange below is written for four channels a warp");
+            const bool up16 = lane & 16, up8 = lane & 8;
+            float k0 = up16 ? part[2] : part[0], k1 = up16 ? part[3] : part[1];
+            k0 += __shfl_xor_sync(0xffffffffu, up16 ? part[0] : part[2], 16);
+            k1 += __shfl_xor_sync(0xffffffffu, up16 ? part[1] : part[3], 16);
+            float k = up8 ? k1 : k0;
+            k += __shfl_xor_sync(0xffffffffu, up8 ? k0 : k1, 8);
+            k += __shfl_xor_sync(0xffffffffu, k, 4);
+            k += __shfl_xor_sync(0xffffffffu, k, 2);
+            k += __shfl_xor_sync(0xffffffffu, k, 1);
+            if ((lane & 7) == 0) {
+                const int c = lane >> 3;
+                ys[i * kBlockCols + warp * kCols + c] = k + D * xs[i * kBlockCols + warp * kCols + c];
+            }
+        }
+        if (!y) continue;
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nb * kBlockCols; idx += blockDim.x) {
+            const int i = idx / kBlockCols, c = idx % kBlockCols;
+            if (pb + c < P) y[(size_t)(tb + i) * inner + xoff + c] = ys[idx];
         }
     }
+    if (!write_state) return;
 #pragma unroll
     for (int c = 0; c < kCols; ++c)
 #pragma unroll
@@ -107,6 +141,62 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
             const int n = lane + 32 * r;
             if (n < N && p0 + c < P) st[(size_t)c * N + n] = S[c][r];
         }
+}
+
+// Long entries are cut into segments that run side by side (the recurrence is linear in the state):
+//   1. ssm_scan over the segments as if each began a sequence: segment k's own contribution L_k to its end state;
+//   2. ssm_chain (this kernel): per entry, in order, in_k = carry ; carry = exp(A * sum of dt over k) * carry + L_k,
+//      beginning with the request's state (zeros at position 0) and ending with the request's new state;
+//   3. ssm_scan over the segments once more, each from its true state in_k, for the outputs.
+// seg_state [segments, heads, P, N] holds L_k on entry and in_k on exit. A block takes 256 numbers of one head's state of one entry.
+constexpr int kChainSpan = 256;     // numbers of a head's state a block of the chain takes
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_chain_kernel(float* __restrict__ seg_state, float* __restrict__ state, long long state_stride,
+                 const T* __restrict__ raw_dt, long long lddt, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                 const int* __restrict__ seg_q_start, const int* __restrict__ entry_seg, const int* __restrict__ start_pos,
+                 const int* __restrict__ slot_ids, int heads, int P, int N) {
+    extern __shared__ float decay[];          // one a segment of this entry
+    qi::pdl_wait();
+    const int h = blockIdx.x, e = blockIdx.y;
+    const int s0 = entry_seg[e], s1 = entry_seg[e + 1];
+    const float A = -expf(a_log[h]), bias = dt_bias[h];
+    // eight threads a segment add up its step sizes
+    for (int k0 = s0; k0 < s1; k0 += blockDim.x / 8) {
+        const int k = k0 + (int)threadIdx.x / 8, part = threadIdx.x & 7;
+        float sum = 0.f;
+        if (k < s1)
+            for (int t = seg_q_start[k] + part; t < seg_q_start[k + 1]; t += 8)
+                sum += softplus_f(qi::to_f32<T>(raw_dt[(size_t)t * lddt + h]) + bias);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (k < s1 && part == 0) decay[k - s0] = expf(A * sum);
+    }
+    __syncthreads();
+    const size_t per_head = (size_t)P * N, per_seg = (size_t)heads * per_head;
+    float* st = state + (size_t)slot_ids[e] * state_stride + (size_t)h * per_head;
+    const bool fresh = start_pos[e] == 0;
+    const size_t lo = (size_t)blockIdx.z * kChainSpan, hi = lo + kChainSpan < per_head ? lo + kChainSpan : per_head;
+    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        float carry = fresh ? 0.f : st[i];
+        float* cell = seg_state + (size_t)s0 * per_seg + (size_t)h * per_head + i;
+        for (int k = s0; k < s1; k += 8) {          // eight segments' loads in flight at a time
+            float local[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) local[j] = k + j < s1 ? cell[(size_t)j * per_seg] : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (k + j < s1) {
+                    cell[(size_t)j * per_seg] = carry;
+                    carry = fmaf(decay[k + j - s0], carry, local[j]);
+                }
+            }
+            cell += 8 * per_seg;
+        }
+        st[i] = carry;
+    }
 }
 
 template <typename TZ, typename TO>
@@ -138,11 +228,12 @@ gated_group_rmsnorm_kernel(const float* __restrict__ y, const TZ* __restrict__ z
 
 // xbc [n, >= heads P + 2 groups N] in `dtype` (x | B | C, `ldx` elements a row); raw_dt [n, >= heads] in `dtype`, column h
 // at raw_dt[t * lddt + h]; dt_bias, a_log, d_skip float32 [heads]; state float32, `state_stride` floats from slot to slot,
-// [heads, P, N] in a slot; y float32 [n, heads P]; q_start [entries + 1], start_pos, slot_ids [entries].
+// [heads, P, N] in a slot; y float32 [n, heads P], or null for a pass that wants the end states only; q_start [entries + 1],
+// start_pos, slot_ids [entries]; write_state 0: the end states are not stored.
 extern "C" int qi_ssm_scan(const void* xbc, long long ldx, const void* raw_dt, long long lddt, int dtype, const float* dt_bias,
                            const float* a_log, const float* d_skip, float* state, long long state_stride, float* y,
                            const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
-                           int groups, int P, int N, cudaStream_t stream) {
+                           int groups, int P, int N, int write_state, cudaStream_t stream) {
     QI_REQUIRE(n_entries >= 0 && heads > 0 && groups > 0 && P > 0 && N > 0, "ssm_scan: bad sizes");
     QI_REQUIRE(heads % groups == 0, "ssm_scan: %d heads are not a multiple of %d groups", heads, groups);
     QI_REQUIRE(N <= 256, "ssm_scan: a state of %d rows is above this kernel's 256", N);
@@ -152,10 +243,11 @@ extern "C" int qi_ssm_scan(const void* xbc, long long ldx, const void* raw_dt, l
     if (n_entries == 0) return 0;
     const dim3 grid(heads, n_entries, (P + kWarps * kCols - 1) / (kWarps * kCols)), block(kWarps * 32);
     const int R = (N + 31) / 32;
+    const size_t smem = sizeof(float) * (size_t)kBatch * (2 * (size_t)N + 2 * kWarps * kCols + 2);
 #define QI_SCAN(RR)                                                                                                         \
     QI_DISPATCH_DTYPE(dtype, T, {                                                                                           \
-        qi::launch(ssm_scan_kernel<T, RR>, grid, block, 0, stream, (const T*)xbc, ldx, (const T*)raw_dt, lddt, dt_bias,     \
-                   a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N);               \
+        qi::launch(ssm_scan_kernel<T, RR>, grid, block, smem, stream, (const T*)xbc, ldx, (const T*)raw_dt, lddt, dt_bias,     \
+                   a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N, write_state);  \
     })
     if (R <= 1) QI_SCAN(1);
     else if (R <= 2) QI_SCAN(2);
@@ -163,6 +255,24 @@ extern "C" int qi_ssm_scan(const void* xbc, long long ldx, const void* raw_dt, l
     else QI_SCAN(8);
 #undef QI_SCAN
     return qi::check_launch("ssm_scan");
+}
+
+// seg_state float32 [segments, heads, P, N] (contiguous); state as for ssm_scan; raw_dt as for ssm_scan; seg_q_start
+// [segments + 1]: the segments' first rows; entry_seg [entries + 1]: the entries' first segments; start_pos, slot_ids [entries].
+extern "C" int qi_ssm_chain(float* seg_state, float* state, long long state_stride, const void* raw_dt, long long lddt, int dtype,
+                            const float* dt_bias, const float* a_log, const int* seg_q_start, const int* entry_seg,
+                            const int* start_pos, const int* slot_ids, int n_entries, int max_segments_an_entry, int heads, int P,
+                            int N, cudaStream_t stream) {
+    QI_REQUIRE(n_entries >= 0 && heads > 0 && P > 0 && N > 0 && max_segments_an_entry >= 0, "ssm_chain: bad sizes");
+    QI_REQUIRE(state_stride >= (long long)heads * P * N && lddt >= heads, "ssm_chain: bad layout");
+    QI_REQUIRE(n_entries <= 65535 && max_segments_an_entry <= 8192, "ssm_chain: too many entries or segments");
+    if (n_entries == 0) return 0;
+    QI_DISPATCH_DTYPE(dtype, T, {
+        qi::launch(ssm_chain_kernel<T>, dim3(heads, n_entries, (unsigned)(((size_t)P * N + kChainSpan - 1) / kChainSpan)), dim3(256), sizeof(float) * (size_t)(max_segments_an_entry + 1), stream,
+                   seg_state, state, state_stride, (const T*)raw_dt, lddt, dt_bias, a_log, seg_q_start, entry_seg, start_pos, slot_ids,
+                   heads, P, N);
+    });
+    return qi::check_launch("ssm_chain");
 }
 
 // y float32 [n, width]; z [n, >= width] in z_dtype with `ldz` elements a row; gain float32 [width]; out [n, width] in out_dtype.

@@ -25,7 +25,7 @@ STATUS_NON_FINITE = 4
 STATUS_WAIT_TIMEOUT = 8
 STATUS_BAD_RANGE = 16
 
-ABI_VERSION = 9
+ABI_VERSION = 11
 
 
 def status_names(code: int) -> list:
@@ -100,7 +100,7 @@ def _check(rc: int, name: str) -> None:
         raise KernelError(f"{name}: {library().qi_last_error().decode()}")
 
 
-knock_out = frozenset()   # kernel classes ("gemm", "attention", "norm", "rope", "other") whose launches are left out
+knock_out = frozenset()   # kernel classes ("gemm", "attention", "norm", "rope", "scan", "other") whose launches are left out
 
 
 def _call(cls, name: str, fn, *args) -> None:
@@ -1090,11 +1090,13 @@ def bias_rope_kv(proj, bias, q_out, inv_freq, rot: int, interleaved: bool, posit
           _stream())
 
 
-def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, slot_ids, heads: int, groups: int, P: int, N: int) -> None:
+def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, slot_ids, heads: int, groups: int, P: int, N: int,
+             write_state: bool = True) -> None:
     """The recurrence S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + d_skip x_t with
     dt_t = softplus(raw_t + dt_bias), per head over each entry's tokens. xbc [n, heads P + 2 groups N] holds x | B | C;
     raw_dt [n, heads] may be a block of columns of wider rows; state float32 [slots, heads, P, N] (read at an entry's first
-    token unless it starts its sequence, written after its last); y float32 [n, heads P]."""
+    token unless it starts its sequence, written after its last unless `write_state` is False); y float32 [n, heads P], or
+    None for a pass that wants the end states only."""
     for t, name in ((xbc, "xbc"), (raw_dt, "raw_dt")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"ssm_scan: {name} must be a CUDA tensor with contiguous rows")
@@ -1107,15 +1109,34 @@ def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, 
     _req_state(state, "state", torch.float32)
     if tuple(state.shape[1:]) != (heads, P, N):
         raise KernelError(f"ssm_scan: state {tuple(state.shape)} does not fit [slots, {heads}, {P}, {N}]")
-    _req(y, "y", torch.float32, 2)
-    if tuple(y.shape) != (xbc.shape[0], heads * P):
-        raise KernelError("ssm_scan: y does not fit")
+    if y is not None:
+        _req(y, "y", torch.float32, 2)
+        if tuple(y.shape) != (xbc.shape[0], heads * P):
+            raise KernelError("ssm_scan: y does not fit")
     for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
         _req(t, name, torch.int32, 1)
-    _call("other", "ssm_scan", library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
+    _call("scan", "ssm_scan", library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
           C.c_longlong(raw_dt.stride(0)), _code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state),
           C.c_longlong(state.stride(0)), _ptr(y), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, groups,
-          P, N, _stream())
+          P, N, int(bool(write_state)), _stream())
+
+
+def ssm_chain(seg_state, state, raw_dt, dt_bias, a_log, seg_q_start, entry_seg, start_pos, slot_ids, max_segments: int) -> None:
+    """Between the two passes of a recurrence cut into segments: seg_state [segments, heads, P, N] holds each segment's
+    own contribution to its end state and receives the state each segment begins with; the requests' states
+    (state [slots, heads, P, N]) advance to their entries' ends. seg_q_start [segments + 1], entry_seg [entries + 1]."""
+    _req(seg_state, "seg_state", torch.float32, 4)
+    _req_state(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != tuple(seg_state.shape[1:]) or raw_dt.dim() != 2 or raw_dt.stride(1) != 1:
+        raise KernelError("ssm_chain: shapes do not agree")
+    for t, name in ((seg_q_start, "seg_q_start"), (entry_seg, "entry_seg"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
+        _req(t, name, torch.int32, 1)
+    if seg_q_start.numel() != seg_state.shape[0] + 1 or entry_seg.numel() != start_pos.numel() + 1:
+        raise KernelError("ssm_chain: the segment lists do not fit")
+    heads, P, N = seg_state.shape[1:]
+    _call("scan", "ssm_chain", library().qi_ssm_chain, _ptr(seg_state), _ptr(state), C.c_longlong(state.stride(0)), _ptr(raw_dt),
+          C.c_longlong(raw_dt.stride(0)), _code(raw_dt), _ptr(dt_bias), _ptr(a_log), _ptr(seg_q_start), _ptr(entry_seg),
+          _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), int(max_segments), heads, P, N, _stream())
 
 
 def gated_group_rmsnorm(y, z, gain, eps: float, out, groups: int) -> None:
@@ -1162,7 +1183,7 @@ def moe_route(logits, correction, ids, weights, scale: float) -> None:
         _req(correction, "correction", torch.float32, 1)
         if correction.numel() != E:
             raise KernelError("moe_route: one correction an expert")
-    _call("other", "moe_route", library().qi_moe_route, _ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, E,
+    _call("gemm", "moe_route", library().qi_moe_route, _ptr(logits), _ptr(correction), _ptr(ids), _ptr(weights), n, E,
           ids.shape[1], C.c_float(scale), _stream())
 
 
@@ -1174,7 +1195,7 @@ def moe_group(ids, n_experts: int, offsets, order, place, tiles) -> None:
     pairs = ids.numel()
     if offsets.numel() != n_experts + 1 or order.numel() != pairs or place.numel() != pairs or tiles.dim() != 2 or tiles.shape[1] != 3:
         raise KernelError("moe_group: shapes do not agree")
-    _call("other", "moe_group", library().qi_moe_group, _ptr(ids), pairs, n_experts, moe_tile_rows(), tiles.shape[0], _ptr(offsets),
+    _call("gemm", "moe_group", library().qi_moe_group, _ptr(ids), pairs, n_experts, moe_tile_rows(), tiles.shape[0], _ptr(offsets),
           _ptr(order), _ptr(place), _ptr(tiles), _stream())
 
 
@@ -1189,7 +1210,32 @@ def moe_gemm(x, w, y, tiles, order, top: int, gather: bool) -> None:
     if x.shape[1] != K or y.shape[1] != N:
         raise KernelError(f"moe_gemm: shapes do not agree: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     _call("gemm", "moe_gemm", library().qi_moe_gemm, _ptr(x), _code(x), _ptr(w), _code(w), _ptr(y), _code(y), _ptr(tiles),
-          tiles.shape[0], _ptr(order), top, int(bool(gather)), N, K, C.c_longlong(K), C.c_longlong(N), _stream())
+          tiles.shape[0], _ptr(order), top, int(bool(gather)), N, K, C.c_longlong(K), C.c_longlong(N), x.shape[0], y.shape[0],
+          w.shape[0], _stream())
+
+
+def moe_gather(x, order, top: int, out) -> None:
+    """out[i] = x[order[i] // top]: the tokens' rows in the experts' order. x [n, K]; out [pairs, K]."""
+    _req(x, "x", ndim=2)
+    _req(out, "out", x.dtype, 2)
+    _req(order, "order", torch.int32)
+    if out.shape[1] != x.shape[1] or order.numel() != out.shape[0]:
+        raise KernelError("moe_gather: shapes do not agree")
+    _call("gemm", "moe_gather", library().qi_moe_gather, _ptr(x), _code(x), _ptr(order), top, _ptr(out), out.shape[0], x.shape[0],
+          x.shape[1], _stream())
+
+
+def moe_gemm_by_expert(x, w, y, bounds, status) -> None:
+    """y[rows of expert e] = x[rows of expert e] . w[e]^T through the tcgen05 product, one launch an expert. x [pairs, K]
+    in the experts' order, w [E, N, K], y [pairs, N], bfloat16; bounds: E + 1 ascending row numbers, on the HOST."""
+    _req(x, "x", torch.bfloat16, 2)
+    _req(w, "w", torch.bfloat16, 3)
+    _req(y, "y", torch.bfloat16, 2)
+    E, N, K = w.shape
+    if x.shape[1] != K or y.shape[1] != N or x.shape[0] != y.shape[0] or len(bounds) != E + 1 or bounds[-1] > x.shape[0]:
+        raise KernelError("moe_gemm_by_expert: shapes do not agree")
+    arr = (C.c_int * (E + 1))(*bounds)
+    _call("gemm", "moe_gemm_by_expert", library().qi_moe_gemm_by_expert, _ptr(x), _ptr(w), _ptr(y), arr, E, N, K, _ptr(status), _stream())
 
 
 def moe_combine(y, place, weights, shared, out) -> None:
@@ -1206,7 +1252,7 @@ def moe_combine(y, place, weights, shared, out) -> None:
         _req(shared, "shared", y.dtype, 2)
         if shared.shape != out.shape:
             raise KernelError("moe_combine: the shared output does not fit")
-    _call("other", "moe_combine", library().qi_moe_combine, _ptr(y), _code(y), _ptr(place), _ptr(weights), _ptr(shared), _ptr(out),
+    _call("gemm", "moe_combine", library().qi_moe_combine, _ptr(y), _code(y), _ptr(place), _ptr(weights), _ptr(shared), _ptr(out),
           _code(out), n, top, width, _stream())
 
 

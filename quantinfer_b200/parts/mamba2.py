@@ -65,6 +65,32 @@ class Mamba2(Part):
         s = self.spec
         return StateNeed((self.conv_floats + s.heads * s.head_dim * s.state,), torch.float32)
 
+    SEGMENT = 64          # tokens a segment of a long entry
+    SEGMENT_FROM = 192    # entries shorter than this run in one piece
+
+    def _segments(self, batch):
+        """The step's entries cut into segments, when one of them is long and the step runs once (a step that may be
+        replayed from a CUDA graph holds single tokens and has no host-side lists): (first rows of the segments, first
+        segments of the entries, zeros, ones, scratch rows, most segments an entry) on the device, shared by the
+        step's layers through `batch.extra`."""
+        if batch.extra.get("graph") or batch.max_q_len < self.SEGMENT_FROM:
+            return None
+        if "ssm_segments" not in batch.extra:
+            starts, entry_seg, longest = [], [0], 0
+            q = batch.h_q_start
+            for a, b in zip(q[:-1], q[1:]):
+                cuts = list(range(a, b, self.SEGMENT)) if b - a >= self.SEGMENT_FROM else [a]
+                starts += cuts
+                entry_seg.append(len(starts))
+                longest = max(longest, len(cuts))
+            n_seg = len(starts)
+            host = torch.tensor(starts + [q[-1]] + entry_seg + [0] * n_seg + [1] * n_seg + list(range(n_seg)), dtype=torch.int32)
+            dev = host.to(batch.q_start.device, non_blocking=True)
+            o = [n_seg + 1, n_seg + 1 + len(entry_seg)]
+            batch.extra["ssm_segments"] = (dev[:o[0]], dev[o[0]:o[1]], dev[o[1]:o[1] + n_seg], dev[o[1] + n_seg:o[1] + 2 * n_seg],
+                                           dev[o[1] + 2 * n_seg:], longest)
+        return batch.extra["ssm_segments"]
+
     def forward(self, x, batch, cache):
         s = self.spec
         n = x.shape[0]
@@ -76,8 +102,21 @@ class Mamba2(Part):
         kernels.short_conv(proj[:, self.inner:self.inner + self.channels], self.conv_w, conv_state, [xbc], None, batch.token_req,
                            batch.q_start, batch.start_pos, batch.slot_ids, residual=False, bias=self.conv_b, act="silu")
         y = torch.empty((n, self.inner), dtype=torch.float32, device=x.device)
-        kernels.ssm_scan(xbc, proj[:, self.inner + self.channels:], self.dt_bias, self.a_log, self.d_skip, ssm_state, y,
-                         batch.q_start, batch.start_pos, batch.slot_ids, s.heads, s.groups, s.head_dim, s.state)
+        raw_dt = proj[:, self.inner + self.channels:]
+        seg = self._segments(batch)
+        if seg is None:
+            kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, ssm_state, y,
+                             batch.q_start, batch.start_pos, batch.slot_ids, s.heads, s.groups, s.head_dim, s.state)
+        else:
+            # long entries: segments side by side (see csrc/ssm.cu): each from zero, the chain of their states, each again
+            seg_q_start, entry_seg, zeros, ones, rows, longest = seg
+            local = torch.empty((rows.numel(), s.heads, s.head_dim, s.state), dtype=torch.float32, device=x.device)
+            kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, local, None, seg_q_start, zeros, rows,
+                             s.heads, s.groups, s.head_dim, s.state)
+            kernels.ssm_chain(local, ssm_state, raw_dt, self.dt_bias, self.a_log, seg_q_start, entry_seg, batch.start_pos,
+                              batch.slot_ids, longest)
+            kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, local, y, seg_q_start, ones, rows,
+                             s.heads, s.groups, s.head_dim, s.state, write_state=False)
         g = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_rmsnorm(y, proj[:, :self.inner], self.gain, s.norm_eps, g, s.norm_groups)
         return self.o(g, keep_partials=True)

@@ -9,10 +9,14 @@
     w_k     = s_k / (sum of the chosen s + 1e-20) * router_scale
     y       = sum_k w_k expert_k(x)  (+ shared(x))
 
-The tokens are grouped by expert on the device (no count ever crosses to the host, so the step can sit in a CUDA
-graph): the (token, choice) pairs are sorted by expert, each expert's rows form tiles of their own, and ONE grouped
-launch per projection runs every expert over exactly its rows. The experts' matrices are stacked [experts, out, in]
-at load. A row's result does not depend on what else the expert got, so a token's output is the same in any batch.
+The tokens are grouped by expert on the device: the (token, choice) pairs are sorted by expert, each expert's rows
+form tiles of their own, and ONE grouped launch per projection runs every expert over exactly its rows; no count
+crosses to the host, so the step can sit in a CUDA graph. The experts' matrices are stacked [experts, out, in] at
+load. A row's result does not depend on what else the expert got, so a token's output is the same in any batch.
+
+A step of many tokens (a prompt or a long portion; never a step that is being captured) instead reads the experts'
+row counts on the host, once, gathers the rows into the experts' order and runs each expert's rows through the
+framework's tcgen05 product, which is several times faster than the grouped mma.sync kernel at such sizes.
 """
 
 from __future__ import annotations
@@ -89,6 +93,14 @@ class MoE(Part):
         if self.shared is not None:
             self.shared.load(tensors)
 
+    ROWS_AN_EXPERT = 128      # from this many rows an expert (on average) a step goes expert by expert
+
+    def _by_expert(self, x, pairs: int) -> bool:
+        s = self.spec
+        return (x.dtype == torch.bfloat16 and self.w_gate_up.dtype == torch.bfloat16 and not kernels.knock_out
+                and pairs >= self.ROWS_AN_EXPERT * s.experts and s.hidden_size % 8 == 0 and s.expert.intermediate_size % 8 == 0
+                and not torch.cuda.is_current_stream_capturing())
+
     def forward(self, x):
         s = self.spec
         n, dev = x.shape[0], x.device
@@ -103,11 +115,19 @@ class MoE(Part):
         tiles = torch.empty((min(pairs, pairs // kernels.moe_tile_rows() + s.experts), 3), dtype=torch.int32, device=dev)
         kernels.moe_group(ids, s.experts, offsets, order, place, tiles)
         gu = torch.empty((pairs, 2 * ff), dtype=x.dtype, device=dev)
-        kernels.moe_gemm(x, self.w_gate_up, gu, tiles, order, s.top, gather=True)
         a = torch.empty((pairs, ff), dtype=x.dtype, device=dev)
-        kernels.glu_clamped(gu, a, s.expert.limit, s.expert.alpha)
         y = torch.empty((pairs, s.hidden_size), dtype=x.dtype, device=dev)
-        kernels.moe_gemm(a, self.w_down, y, tiles, order, s.top, gather=False)
+        if self._by_expert(x, pairs):
+            bounds = offsets.tolist()          # the one place where such a step waits for the device
+            xs = torch.empty((pairs, s.hidden_size), dtype=x.dtype, device=dev)
+            kernels.moe_gather(x, order, s.top, xs)
+            kernels.moe_gemm_by_expert(xs, self.w_gate_up, gu, bounds, self.runtime.status)
+            kernels.glu_clamped(gu, a, s.expert.limit, s.expert.alpha)
+            kernels.moe_gemm_by_expert(a, self.w_down, y, bounds, self.runtime.status)
+        else:
+            kernels.moe_gemm(x, self.w_gate_up, gu, tiles, order, s.top, gather=True)
+            kernels.glu_clamped(gu, a, s.expert.limit, s.expert.alpha)
+            kernels.moe_gemm(a, self.w_down, y, tiles, order, s.top, gather=False)
         shared = self.shared.forward(x) if self.shared is not None else None
         out = torch.empty((n, s.hidden_size), dtype=x.dtype, device=dev)
         kernels.moe_combine(y, place, weights, shared, out)

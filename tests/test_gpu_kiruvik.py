@@ -29,7 +29,7 @@ DEV = "cuda:0"
 TOL_F32 = 2e-5
 TOL_BF16 = {"P": 0.12, "Q": 0.2, "R": 0.12}
 BF16_ROWS_BEYOND = 0.04
-LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 150, 5], "R": [50, 33, 80, 17, 64, 9]}
+LENGTHS = {"P": [70, 45, 100, 33, 2, 64, 17, 1], "Q": [130, 64, 97, 33, 260, 5], "R": [50, 33, 80, 17, 64, 9]}
 
 
 @pytest.fixture(scope="module")
@@ -308,6 +308,20 @@ def test_the_recurrent_mixer_however_the_sequence_is_cut(tmp_path, cut, shape):
     assert float((ref2[40] - ref[40]).abs().max()) > 1e-3
 
 
+@pytest.mark.parametrize("cuts", [[500], [250, 250], [193, 7, 300], [40, 460]])
+def test_long_entries_run_as_segments_side_by_side(tmp_path, cuts):
+    """Entries of 192 tokens and more are cut into segments of 64 that run at once, chained through their states; a
+    portion's last segment is short, and the request's state must come out as if the tokens had run in a row."""
+    entry = layer(ssm(3, 8, 33, 3, 3, 1), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", seed=19, max_tokens=1024)
+    torch.manual_seed(14)
+    x = torch.randn(sum(cuts) + 30, 24)
+    ref = plain.mamba2(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.", 1e-6)
+    got = _run_mixer(eng, x, cuts + [1] * 30)
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 1e-4, (int(err.argmax()), float(err.max()))
+
+
 def test_the_recurrent_state_over_three_hundred_single_steps_in_bfloat16(tmp_path):
     entry = layer(ssm(2, 16, 16, 1, 4, 1), None)
     eng, cfg, w = _one_layer(tmp_path, entry, 32, "bfloat16", seed=10)
@@ -348,6 +362,23 @@ def test_feed_forwards_alone_and_a_token_in_any_company(tmp_path, dtype, mlp):
         # the limits matter in this test
         loose = dict(mlp, expert=dict(mlp["expert"], limit=1e9))
         assert float((plain.moe(x.double(), loose, w, "l0.mlp.") - ref).abs().max()) > 0.01
+
+
+def test_a_step_of_many_tokens_runs_the_experts_one_by_one(tmp_path):
+    """From 128 rows an expert on average the mixture reads the experts' counts on the host and runs each expert's rows
+    through the dense tensor-core product: the same values as the grouped launch, up to the order of sums."""
+    entry = layer(attn(2, 1, 8, 8, 0), moe(4, 2, 1.5, 32, 1.0, shared=(16, 1.0)))
+    eng, cfg, w = _one_layer(tmp_path, entry, 64, "bfloat16", seed=13)
+    ffn = eng.model.blocks[0].ffn
+    torch.manual_seed(8)
+    x = torch.randn(300, 64).to(torch.bfloat16)
+    assert ffn._by_expert(x.to(DEV), 600) and not ffn._by_expert(x[:100].to(DEV), 200)
+    big = ffn.forward(x.to(DEV)).float().cpu()
+    small = torch.cat([ffn.forward(x[i:i + 100].to(DEV)) for i in (0, 100, 200)]).float().cpu()
+    ref = plain.moe(x.double(), entry["mlp"], w, "l0.mlp.")
+    assert float((big - small).abs().max()) < 0.05
+    err = (big.double() - ref).abs().max(dim=1).values
+    assert float(err.median()) < 0.03 and int((err > 0.15).sum()) <= 6
 
 
 # ---------------------------------------------------------------- whole models, replayed
