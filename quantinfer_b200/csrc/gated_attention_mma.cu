@@ -10,7 +10,8 @@
 // consecutive query rows of ONE step entry and one query head (the tiles are found on the device from
 // q_start, so the launch can sit in a CUDA graph), walks the keys its rows can see in tiles of 64 that
 // start at multiples of 64 of the ABSOLUTE position (so a row's sums do not depend on where a prompt
-// was cut), with the softmax evaluated online. Keys before the first visible one are zero-filled and
+// was cut), with the softmax evaluated online; the next tile is requested with cp.async into a second buffer
+// while the current one is multiplied. Keys before the first visible one are zero-filled and
 // never looked up: their pages may have gone back to the pool. Head sizes are padded with zeros to the
 // next of 32, 64, 96, 128 in shared memory.
 #include "common.cuh"
@@ -48,6 +49,23 @@ __device__ __forceinline__ void fill_tile(qi::bf16* dst, int stride, int rows, i
     }
 }
 
+// The same with cp.async (16 bytes a request; a refused row or a padding column is zero-filled by a request of
+// zero source bytes), for tiles that land while the tile before them is multiplied.
+template <typename RowPtr>
+__device__ __forceinline__ void fill_tile_async(qi::bf16* dst, int stride, int rows, int width, int padded, const qi::bf16* any, RowPtr row_ptr) {
+    // two threads a row (64 rows, 128 threads): the row's page is looked up once, its 16-byte pieces are dealt out in turn
+    static_assert(kThreads == 2 * kKT, "two threads a row");
+    const int r = threadIdx.x >> 1;
+    if (r >= rows) return;
+    const qi::bf16* src = row_ptr(r);
+    const uint32_t d0 = (uint32_t)__cvta_generic_to_shared(dst + (size_t)r * stride);
+    for (int c = threadIdx.x & 1; c * 8 < padded; c += 2) {
+        const bool real = src && c * 8 < width;
+        const int bytes = real ? 16 : 0;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d0 + c * 16), "l"(real ? (const void*)(src + c * 8) : (const void*)any), "r"(bytes) : "memory");
+    }
+}
+
 template <int DK, int DV>
 __global__ void __launch_bounds__(kThreads)
 gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict__ out, const qi::bf16* __restrict__ k_pages,
@@ -58,8 +76,8 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int SK = DK + kPad, SV = DV + kPad;
     qi::bf16* Qs = reinterpret_cast<qi::bf16*>(smem_raw);       // [kQT][SK]
-    qi::bf16* Ks = Qs + kQT * SK;                                // [kKT][SK]
-    qi::bf16* Vs = Ks + kKT * SK;                                // [kKT][SV]
+    qi::bf16* Kbuf = Qs + kQT * SK;                              // 2 x [kKT][SK]
+    qi::bf16* Vbuf = Kbuf + 2 * kKT * SK;                        // 2 x [kKT][SV]
 
     qi::pdl_wait();
     // which tile of which entry this CTA takes
@@ -115,8 +133,7 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
     for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
     bool bad_page = false;
-    for (int t0 = lo_min / kKT * kKT; t0 <= hi; t0 += kKT) {
-        __syncthreads();
+    auto request_tile = [&](int t0, int buf) {
         auto page_row = [&](int r, const qi::bf16* pages, int width) -> const qi::bf16* {
             const int key = t0 + r;
             if (key < lo_min || key > hi) return nullptr;
@@ -124,9 +141,23 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
             if (page < 0 || page >= num_pages) { bad_page = true; return nullptr; }
             return pages + (((size_t)page * nkv + hk) * page_size + (key % page_size)) * (size_t)width;
         };
-        fill_tile(Ks, SK, kKT, d, DK, [&](int r) { return page_row(r, k_pages, d); });
-        fill_tile(Vs, SV, kKT, dv, DV, [&](int r) { return page_row(r, v_pages, dv); });
+        fill_tile_async(Kbuf + (size_t)buf * kKT * SK, SK, kKT, d, DK, k_pages, [&](int r) { return page_row(r, k_pages, d); });
+        fill_tile_async(Vbuf + (size_t)buf * kKT * SV, SV, kKT, dv, DV, k_pages, [&](int r) { return page_row(r, v_pages, dv); });
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int t_first = lo_min / kKT * kKT;
+    request_tile(t_first, 0);
+    int buf = 0;
+    for (int t0 = t_first; t0 <= hi; t0 += kKT, buf ^= 1) {
+        if (t0 + kKT <= hi) {            // the next tile lands while this one is multiplied
+            request_tile(t0 + kKT, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
+        const qi::bf16* Ks = Kbuf + (size_t)buf * kKT * SK;
+        const qi::bf16* Vs = Vbuf + (size_t)buf * kKT * SV;
 
         float s[kKT / 8][4];
 #pragma unroll
@@ -187,6 +218,7 @@ gated_attention_mma_kernel(const qi::bf16* __restrict__ q, qi::bf16* __restrict_
                 mma_bf16(o[2 * n2 + 1], pa, b2, b3);
             }
         }
+        __syncthreads();                 // every warp is done with this buffer before the tile after next is requested into it
     }
     if (bad_page && status) atomicOr(status, qi::kStatusBadPage);
     lA += __shfl_xor_sync(0xffffffffu, lA, 1); lA += __shfl_xor_sync(0xffffffffu, lA, 2);
@@ -219,7 +251,7 @@ int launch_one(dim3 grid, cudaStream_t stream, const void* q, void* out, const v
                const int* block_table, int max_blocks, int page_size, int num_pages, const int* q_start, const int* start_pos,
                int n_entries, int nq, int nkv, int d, int dv, float scale_log2e, int window, int chunk, const void* gate,
                long long ldg, int* status) {
-    const size_t smem = sizeof(qi::bf16) * ((size_t)(kQT + kKT) * (DK + kPad) + (size_t)kKT * (DV + kPad));
+    const size_t smem = sizeof(qi::bf16) * ((size_t)(kQT + 2 * kKT) * (DK + kPad) + (size_t)2 * kKT * (DV + kPad));
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
         cudaFuncSetAttribute(gated_attention_mma_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -25,7 +25,7 @@
 
 namespace {
 
-constexpr int kCols = 4;       // channels a warp
+constexpr int kCols = 8;       // channels a warp
 constexpr int kWarps = 4;      // warps a block
 constexpr int kBatch = 16;     // tokens whose operands are staged in shared memory at a time
 
@@ -72,11 +72,13 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
     for (int tb = t0; tb < t1; tb += kBatch) {
         const int nb = min(kBatch, t1 - tb);
         __syncthreads();                              // the batch before is consumed and written
-        for (int idx = threadIdx.x; idx < nb * N; idx += blockDim.x) {
-            const int i = idx / N, n = idx % N;
-            const T* row = xbc + (size_t)(tb + i) * ldx;
-            Bs[i * N + n] = qi::to_f32<T>(row[boff + n]);
-            Cs[i * N + n] = qi::to_f32<T>(row[coff + n]);
+        for (int i = warp; i < nb; i += kWarps) {     // a warp brings whole rows: no division in the loop
+            const T* rb = xbc + (size_t)(tb + i) * ldx + boff;
+            const T* rc = xbc + (size_t)(tb + i) * ldx + coff;
+            for (int n = lane; n < N; n += 32) {
+                Bs[i * N + n] = qi::to_f32<T>(rb[n]);
+                Cs[i * N + n] = qi::to_f32<T>(rc[n]);
+            }
         }
         for (int idx = threadIdx.x; idx < nb * kBlockCols; idx += blockDim.x) {
             const int i = idx / kBlockCols, c = idx % kBlockCols;
@@ -109,21 +111,24 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
                 }
             }
             if (!y) continue;          // a pass that is after the end state only
-            // the four channels' sums over the warp in six exchanges: halves trade channels, then quarters, then the
-            // eight lanes that are left add up; lanes 0, 8, 16 and 24 end up with channels 0, 1, 2 and 3
-            static_assert(kCols == 4, "the exchange below is written for four channels a warp");
+            // four channels' sums over the warp in six exchanges: halves trade channels, then quarters, then the
+            // eight lanes that are left add up; lanes 0, 8, 16 and 24 end up with channels 0, 1, 2 and 3 of the four
+            static_assert(kCols % 4 == 0, "the exchange below takes four channels at a time");
             const bool up16 = lane & 16, up8 = lane & 8;
-            float k0 = up16 ? part[2] : part[0], k1 = up16 ? part[3] : part[1];
-            k0 += __shfl_xor_sync(0xffffffffu, up16 ? part[0] : part[2], 16);
-            k1 += __shfl_xor_sync(0xffffffffu, up16 ? part[1] : part[3], 16);
-            float k = up8 ? k1 : k0;
-            k += __shfl_xor_sync(0xffffffffu, up8 ? k0 : k1, 8);
-            k += __shfl_xor_sync(0xffffffffu, k, 4);
-            k += __shfl_xor_sync(0xffffffffu, k, 2);
-            k += __shfl_xor_sync(0xffffffffu, k, 1);
-            if ((lane & 7) == 0) {
-                const int c = lane >> 3;
-                ys[i * kBlockCols + warp * kCols + c] = k + D * xs[i * kBlockCols + warp * kCols + c];
+#pragma unroll
+            for (int q4 = 0; q4 < kCols; q4 += 4) {
+                float k0 = up16 ? part[q4 + 2] : part[q4], k1 = up16 ? part[q4 + 3] : part[q4 + 1];
+                k0 += __shfl_xor_sync(0xffffffffu, up16 ? part[q4] : part[q4 + 2], 16);
+                k1 += __shfl_xor_sync(0xffffffffu, up16 ? part[q4 + 1] : part[q4 + 3], 16);
+                float k = up8 ? k1 : k0;
+                k += __shfl_xor_sync(0xffffffffu, up8 ? k0 : k1, 8);
+                k += __shfl_xor_sync(0xffffffffu, k, 4);
+                k += __shfl_xor_sync(0xffffffffu, k, 2);
+                k += __shfl_xor_sync(0xffffffffu, k, 1);
+                if ((lane & 7) == 0) {
+                    const int c = warp * kCols + q4 + (lane >> 3);
+                    ys[i * kBlockCols + c] = k + D * xs[i * kBlockCols + c];
+                }
             }
         }
         if (!y) continue;
