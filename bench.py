@@ -564,12 +564,17 @@ def compare_kiruvik(args):
             for cls in work:
                 d_alone, _ = timed([c for c in every if c != cls])
                 _, p_without = timed([cls])
-                c = {"decode_alone_ms": round(d_alone, 4), "prefill_left_out_ms": round(pre_ms - p_without, 4)}
-                if d_alone > 0 and pre_ms > p_without:
+                # a prompt step with a class left out runs its other kernels on whatever the buffers hold; a router then
+                # sends every token to the same few experts and the step gets SLOWER: such a difference says nothing and
+                # is left out (the kernels' own times are in profiles/)
+                left = pre_ms - p_without if pre_ms > p_without else None
+                c = {"decode_alone_ms": round(d_alone, 4), "prefill_left_out_ms": round(left, 4) if left is not None else None}
+                if d_alone > 0:
                     c["decode_frac_hbm"] = round(work[cls][0] / (d_alone * 1e-3) / 1e9 / hbm, 4)
-                    c["prefill_frac_burst"] = round(work[cls][1] / ((pre_ms - p_without) * 1e-3) / 1e12 / burst, 4)
+                if left is not None:
+                    c["prefill_frac_burst"] = round(work[cls][1] / (left * 1e-3) / 1e12 / burst, 4)
                 rest[0] -= d_alone
-                rest[1] -= pre_ms - p_without
+                rest[1] -= left or 0.0
                 row["classes"][cls] = c
                 print(f"[compare] {entry['name']} {cls}: {c}", file=sys.stderr, flush=True)
             row["classes"]["rest"] = {"decode_ms": round(rest[0], 4), "prefill_ms": round(rest[1], 4)}
