@@ -502,12 +502,12 @@ def kiruvik_entries(size):
     att = {"heads": z["heads"], "kv_heads": z["kv"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
            "rot": {"base": 500000.0, "dims": 64}, "mask": {"size": KIRUVIK_CHUNK}}
     rec = {"heads": z["sheads"], "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
-    mix = {"kind": "moe", "router": {"experts": z["experts"], "top": KIRUVIK_TOP, "scale": 2.5},
+    mix = {"kind": "moe", "router": {"experts": z["experts"], "top": KIRUVIK_TOP, "scale": 2.0},
            "expert": {"ff": z["eff"], "limit": 7.0}, "shared": {"ff": z["sff"], "limit": 7.0}}
     den = {"kind": "dense", "ff": z["ff"]}
     layers = [{"type": "attention", "mixer": att, "mlp": den}, {"type": "mamba2", "mixer": rec, "mlp": mix},
               {"type": "attention", "mixer": att, "mlp": mix}, {"type": "mamba2", "mixer": rec, "mlp": den}]
-    new = dict(architecture="Kiruvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, residual_mult=0.5, layers=layers)
+    new = dict(architecture="Kiruvik", vocab=COMPARE_VOCAB, width=z["width"], norm={"eps": 1e-6}, residual_mult=0.6, layers=layers)
     dense = dict(_COMMON, vocab_size=COMPARE_VOCAB, hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=COMPARE_LAYERS,
                  num_attention_heads=z["heads"], num_key_value_heads=z["kv"], head_dim=128)
     common = dict(seed=5, prompt_len=COMPARE_PROMPT, context=4096, batch=COMPARE_BATCH, points=())

@@ -45,7 +45,7 @@ CONFIGS = {
     # multiple of the page; a layer without chunks and without feed-forward; two groups and three norm parts in the
     # recurrent layer; a loop that starts after the first layer
     "P": {"architecture": "Kiruvik", "vocab": 131, "width": 40, "norm": {"eps": 3e-6}, "residual_mult": 0.7,
-          "loop": {"start": 1, "stop": 3, "times": 2},
+          "loop": {"start": 1, "stop": 3, "times": 3},
           "layers": [layer(attn(3, 3, 10, 6, 4, chunk=9, base=300.0), dense(56)),
                      layer(ssm(4, 6, 5, 2, 4, 3), moe(5, 3, 1.7, 12, 0.8, shared=(20, 1.3))),
                      layer(attn(6, 2, 6, 14, 6, chunk=21), moe(3, 3, 0.9, 10, 2.0)),
@@ -56,11 +56,11 @@ CONFIGS = {
           "layers": [layer(ssm(2, 32, 64, 1, 2, 1), dense(96)),
                      layer(attn(4, 1, 32, 16, 32, chunk=16, base=250000.0), moe(8, 1, 2.0, 32, 1.0)),
                      layer(attn(4, 4, 16, 32, 8, chunk=48), dense(128))]},
-    # one tap (a convolution without state); a state of more rows than a warp; every layer looped three times;
+    # one tap (a convolution without state); a state of more rows than a warp; every layer looped twice;
     # a chunk of one page; two rotated coordinates
-    "R": {"architecture": "Kiruvik", "vocab": 97, "width": 48, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
-          "loop": {"start": 0, "stop": 2, "times": 3},
-          "layers": [layer(ssm(3, 8, 33, 3, 1, 2), moe(6, 2, 2.5, 16, 1.0, shared=(8, 0.5))),
+    "R": {"architecture": "Kiruvik", "vocab": 97, "width": 48, "norm": {"eps": 1e-6}, "residual_mult": 0.8,
+          "loop": {"start": 0, "stop": 2, "times": 2},
+          "layers": [layer(ssm(3, 8, 33, 3, 1, 2), moe(6, 2, 1.3, 16, 1.5, shared=(8, 0.5))),
                      layer(attn(2, 2, 8, 8, 2, chunk=8, base=50.0), dense(40))]},
 }
 PAGE_SIZES = {"P": 8, "Q": 16, "R": 8}

@@ -143,7 +143,7 @@ def test_router_choice_and_weights(E, top):
 
 
 @pytest.mark.parametrize("impl", ["mma", "generic"])
-@pytest.mark.parametrize("d, dv, H, G, chunk, window, page", [(96, 96, 4, 2, 64, 0, 64), (16, 32, 4, 1, 20, 0, 8), (128, 64, 2, 2, 0, 0, 16),
+@pytest.mark.parametrize("d, dv, H, G, chunk, window, page", [(96, 80, 6, 2, 48, 0, 64), (16, 32, 4, 1, 20, 0, 8), (128, 64, 2, 2, 0, 0, 16),
                                                              (40, 8, 6, 3, 100, 37, 32), (64, 128, 8, 2, 7, 0, 64), (24, 24, 1, 1, 0, 50, 8)])
 def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, chunk, window, page):
     """Decode tokens in front of prompt portions in one launch, contexts of unequal length on pages handed out in
@@ -276,7 +276,7 @@ def test_attention_rounds_only_where_it_may(tmp_path, dtype):
     """The whole head rotated, one kv head, keys smaller than values, positions beyond a thousand (angles in 32-bit)."""
     from quantinfer_b200.engine import StepEntry
 
-    entry = layer(attn(4, 1, 16, 32, 16, chunk=64, base=20000.0), None)
+    entry = layer(attn(4, 1, 16, 32, 16, chunk=80, base=30000.0), None)
     eng, cfg, w = _one_layer(tmp_path, entry, 32, dtype, page_size=16, seed=5, max_tokens=1152)
     T = 1100
     torch.manual_seed(6)

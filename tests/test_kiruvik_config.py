@@ -28,13 +28,13 @@ def test_config_round_trip_and_tensor_list(name):
 
 def test_run_order_of_a_loop_and_its_cache_entries():
     spec = config_from_dict(CONFIGS["P"]).to_model_spec()
-    assert [(c.layer, c.reenter) for c in spec.order] == [(0, False), (1, True), (2, False), (1, True), (2, False), (3, False)]
-    assert [c.cache for c in spec.order] == list(range(6)) and all(c.writes_cache for c in spec.order)
+    assert [(c.layer, c.reenter) for c in spec.order] == [(0, False), (1, True), (2, False), (1, True), (2, False), (1, True), (2, False), (3, False)]
+    assert [c.cache for c in spec.order] == list(range(8)) and all(c.writes_cache for c in spec.order)
     assert spec.reentry is not None and spec.reentry.weight_name == "loop.in"
     spec = config_from_dict(CONFIGS["Q"]).to_model_spec()
     assert spec.reentry is None and not any(c.reenter for c in spec.order)
     spec = config_from_dict(CONFIGS["R"]).to_model_spec()
-    assert [(c.layer, c.reenter) for c in spec.order] == [(0, True), (1, False)] * 3
+    assert [(c.layer, c.reenter) for c in spec.order] == [(0, True), (1, False)] * 2
 
 
 def test_specs_carry_every_constant_of_the_file():
