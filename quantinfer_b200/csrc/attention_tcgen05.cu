@@ -262,7 +262,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                       int num_pages, const int* __restrict__ q_start, const int* __restrict__ start_pos,
                                       const int* __restrict__ tile_req, const int* __restrict__ tile_q0, int nq, int nkv,
                                       float scale_log2e, int window, int* __restrict__ status, int n_ranges,
-                                      float* __restrict__ ws_o, float* __restrict__ ws_ml) {
+                                      float* __restrict__ ws_o, float* __restrict__ ws_ml, int chunk,
+                                      const qi::bf16* __restrict__ gate, long long ldg) {
     extern __shared__ uint8_t smem_raw[];
     using B = Bars;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -288,7 +289,10 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int pos0 = start_pos[r] + (q0 - q_start[r]);
     const int* table = block_table + (size_t)r * max_blocks;
     const int hi = pos0 + rows_valid;
-    const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    // the first key any of these rows sees: the window's reach and the start of the first row's chunk (chunks are
+    // counted from position 0 of the sequence); later rows' own bounds are applied row by row
+    int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    if (chunk > 0) lo = max(lo, pos0 / chunk * chunk);
     // With n_ranges > 1 the key tiles of these query rows are cut into that many ranges, one CTA each
     // (blockIdx.z); every CTA leaves its rows' reference, sum and accumulator in the workspace and a
     // second kernel merges them. A long context then gives enough CTAs to fill the GPU's last round.
@@ -466,7 +470,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             if (!mbar_wait(bars + B::s_full, u & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             int c_hi = min(min(pos, hi - 1) - t0 + 1, BN);
-            int c_lo = max(lo, window > 0 ? pos - window + 1 : 0) - t0;
+            int c_lo = max(max(lo, window > 0 ? pos - window + 1 : 0), chunk > 0 ? pos / chunk * chunk : 0) - t0;
             if (c_lo < 0) c_lo = 0;
             if (c_hi < 0) c_hi = 0;
             uint32_t sv[BN];
@@ -541,6 +545,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             tc_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             qi::bf16* orow = out + ((size_t)(q0 + row) * nq + h) * D;
+            const qi::bf16* grow = gate ? gate + (size_t)(q0 + row) * ldg + (size_t)h * D : nullptr;
             // the row's 128 columns in two halves, each half's loads in flight together
 #pragma unroll 1
             for (int c0 = 0; c0 < D; c0 += 64) {
@@ -551,6 +556,15 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (row < rows_valid && n_tiles > 0) {
 #pragma unroll
                     for (int i = 0; i < 64; i += 8) {
+                        if (grow) {    // the output gate: each value times sigmoid of its gate logit
+                            const uint4 gv = *reinterpret_cast<const uint4*>(grow + c0 + i);
+                            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const float gl = __uint_as_float((e & 1) ? (gw[e >> 1] & 0xffff0000u) : (gw[e >> 1] << 16));
+                                v[i + e] = __float_as_uint(__uint_as_float(v[i + e]) / (1.f + __expf(-gl)));
+                            }
+                        }
                         uint4 w;
                         w.x = qi_attn::pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
                         w.y = qi_attn::pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
@@ -570,7 +584,8 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M) over the key ranges of a query row, in range order.
 __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
-                                               qi::bf16* __restrict__ out, int nq, int n_ranges) {
+                                               qi::bf16* __restrict__ out, int nq, int n_ranges,
+                                               const qi::bf16* __restrict__ gate, long long ldg) {
     qi::pdl_enter();
     const int h = blockIdx.x;
     const size_t t = blockIdx.y;
@@ -586,7 +601,9 @@ __global__ void attention_prefill_merge_kernel(const float* __restrict__ ws_o, c
             L += ws_ml[(base + s) * 2 + 1] * f;
             O += ws_o[(base + s) * D + col] * f;
         }
-        out[(t * nq + h) * D + col] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        float o = L > 0.f ? O / L : 0.f;
+        if (gate) o = o / (1.f + __expf(-__bfloat162float(gate[t * (size_t)ldg + (size_t)h * D + col])));
+        out[(t * nq + h) * D + col] = __float2bfloat16_rn(o);
     }
 }
 
@@ -635,13 +652,17 @@ extern "C" int qi_attention_prefill_tcgen05_supported(int nq, int nkv, int d, in
 // kernel that has ended), not still being written by a kernel under programmatic dependent launch.
 // Arguments as qi_attention_prefill_tma (the tile lists are cut to 128 query rows), and: n_ranges > 1
 // cuts every query tile's keys into that many ranges over separate CTAs, merged by a second kernel;
-// `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats.
-extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void* k_pages, const void* v_pages,
-                                            const int* block_table, int max_blocks, int page_size, int num_pages,
-                                            const int* q_start, const int* start_pos, const int* tile_req,
-                                            const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
-                                            float scale, int window, int n_ranges, float* workspace, int* status,
-                                            cudaStream_t stream) {
+// `workspace` must then hold n_tokens * nq * n_ranges * (128 + 2) floats. chunk > 0: a query at position i sees
+// key j <= i only if floor(i / chunk) = floor(j / chunk). gate (or null): bfloat16 [n_tokens, nq * 128] with rows
+// `ldg` elements apart; the output is multiplied element by element with its sigmoid.
+extern "C" int qi_attention_prefill_tcgen05_ex(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                               const int* block_table, int max_blocks, int page_size, int num_pages,
+                                               const int* q_start, const int* start_pos, const int* tile_req,
+                                               const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
+                                               float scale, int window, int chunk, const void* gate, long long ldg,
+                                               int n_ranges, float* workspace, int* status, cudaStream_t stream) {
+    QI_REQUIRE(chunk >= 0 && (!gate || (((uintptr_t)gate & 15) == 0 && ldg % 8 == 0 && ldg >= (long long)nq * D)),
+               "attention_prefill_tcgen05: a gate must be 16-byte aligned with rows a multiple of 8 elements apart");
     QI_REQUIRE(qi_attention_prefill_tcgen05_supported(nq, nkv, d, page_size, max_blocks),
                "attention_prefill_tcgen05: heads %d/%d of size %d with %d pages of %d per request are not covered", nq, nkv,
                d, max_blocks, page_size);
@@ -668,14 +689,26 @@ extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void
     float* ws_ml = workspace ? workspace + (size_t)n_tokens * nq * n_ranges * D : nullptr;
     qi::launch(attention_prefill_tcgen05_kernel, dim3(nq, n_tiles, n_ranges), dim3(kThreads), kSmemBytes, stream, mq, mk, mv,
                (qi::bf16*)out, block_table, max_blocks, page_size, box_rows, num_pages, q_start, start_pos, tile_req,
-               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status, n_ranges, ws_o, ws_ml);
+               tile_q0, nq, nkv, scale * 1.4426950408889634f, window, status, n_ranges, ws_o, ws_ml, chunk,
+               (const qi::bf16*)gate, ldg);
     if (n_ranges > 1) {
         if (int rc = qi::check_launch("attention_prefill_tcgen05")) return rc;
         qi::launch(attention_prefill_merge_kernel, dim3(nq, n_tokens), dim3(128), 0, stream, (const float*)ws_o,
-                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges);
+                   (const float*)ws_ml, (qi::bf16*)out, nq, n_ranges, (const qi::bf16*)gate, ldg);
         return qi::check_launch("attention_prefill_merge");
     }
     return qi::check_launch("attention_prefill_tcgen05");
+}
+
+extern "C" int qi_attention_prefill_tcgen05(const void* q, void* out, const void* k_pages, const void* v_pages,
+                                            const int* block_table, int max_blocks, int page_size, int num_pages,
+                                            const int* q_start, const int* start_pos, const int* tile_req,
+                                            const int* tile_q0, int n_tiles, int n_tokens, int nq, int nkv, int d,
+                                            float scale, int window, int n_ranges, float* workspace, int* status,
+                                            cudaStream_t stream) {
+    return qi_attention_prefill_tcgen05_ex(q, out, k_pages, v_pages, block_table, max_blocks, page_size, num_pages, q_start,
+                                           start_pos, tile_req, tile_q0, n_tiles, n_tokens, nq, nkv, d, scale, window, 0,
+                                           nullptr, 0, n_ranges, workspace, status, stream);
 }
 
 QI_TL_EXPORT(qi_timeline_prefill_attention)

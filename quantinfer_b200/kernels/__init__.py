@@ -377,7 +377,8 @@ def attention_prefill_ranges(n_ctas: int, max_kv_len: int) -> int:
 
 def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos, tile_req, tile_q0,
                       nq, nkv, d, scale: float, window: int, status, use_tma: bool | None = None,
-                      impl: str | None = None, max_kv_len: int = 0, key_ranges: int | None = None) -> None:
+                      impl: str | None = None, max_kv_len: int = 0, key_ranges: int | None = None, chunk: int = 0,
+                      gate=None) -> None:
     """Causal paged GQA flash attention (bfloat16, head size 64 or 128) for spans of any
     length. `tile_req[i]`, `tile_q0[i]`: request index and first flat token of the i-th
     block of up to QUERY_TILE query rows.
@@ -387,7 +388,10 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
     sizes, head size 64 or 128) and "cpasync" (mma.sync, any page size). `impl` forces one;
     the default is the first that takes the geometry. `use_tma` is the older switch between
     the last two. `max_kv_len` (the longest context of the step) lets the tcgen05 kernel cut long
-    contexts into key ranges over more CTAs (`key_ranges` forces a number)."""
+    contexts into key ranges over more CTAs (`key_ranges` forces a number). The tcgen05 kernel alone takes
+    `chunk` (a query sees only the keys of its own chunk of that many positions, counted from the sequence's
+    start) and `gate` (bfloat16 [n, nq d], rows a multiple of 8 elements apart and 16-byte aligned: the output is
+    multiplied with its sigmoid)."""
     if impl is None and use_tma is not None:
         impl = "tma" if use_tma else "cpasync"
     _req(q, "q", torch.bfloat16, 2)
@@ -415,12 +419,19 @@ def attention_prefill(q, out, k_pages, v_pages, block_table, q_start, start_pos,
         if q.shape[0] > 65535:
             ranges = 1
         ws = torch.empty(q.shape[0] * nq * ranges * (d + 2), dtype=torch.float32, device=q.device) if ranges > 1 else None
-        _call('attention', "attention_prefill_tcgen05", library().qi_attention_prefill_tcgen05,
+        ldg = 0
+        if gate is not None:
+            if not gate.is_cuda or gate.dtype != torch.bfloat16 or gate.dim() != 2 or gate.stride(1) != 1 or gate.shape != out.shape:
+                raise KernelError("attention_prefill: the gate must be bfloat16 [n, nq d] with contiguous rows")
+            ldg = gate.stride(0)
+        _call('attention', "attention_prefill_tcgen05", library().qi_attention_prefill_tcgen05_ex,
               _ptr(q), _ptr(out), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), block_table.shape[1],
             k_pages.shape[2], k_pages.shape[0], _ptr(q_start), _ptr(start_pos), _ptr(tile_req), _ptr(tile_q0),
-            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), ranges, _ptr(ws),
-            _ptr(status), _stream())
+            tile_req.numel(), q.shape[0], nq, nkv, d, C.c_float(scale), int(window or 0), int(chunk or 0), _ptr(gate),
+            C.c_longlong(ldg), ranges, _ptr(ws), _ptr(status), _stream())
         return
+    if chunk or gate is not None:
+        raise KernelError(f"attention_prefill: the {impl!r} kernel takes neither a chunk bound nor a gate")
     if impl not in ("tma", "cpasync"):
         raise KernelError(f"attention_prefill: unknown kernel {impl!r}")
     if impl == "tma":
@@ -1256,6 +1267,14 @@ def moe_combine(y, place, weights, shared, out) -> None:
           _code(out), n, top, width, _stream())
 
 
+class _LeadRows:
+    """The single-token entries at the front of a mixed step, as the batch fields the attention kernels read."""
+
+    def __init__(self, batch, lead: int):
+        self.q_start, self.start_pos, self.n_requests = batch.q_start[:lead + 1], batch.start_pos[:lead], lead
+        self.positions, self.token_req = batch.positions[:lead], batch.token_req[:lead]
+
+
 def gated_attention_mma_supported(nq: int, nkv: int, d: int, dv: int) -> bool:
     """Whether the tensor-core kernel for separate key and value sizes takes this geometry (bfloat16 only)."""
     return bool(library().qi_gated_attention_mma_supported(nq, nkv, d, dv))
@@ -1265,7 +1284,21 @@ def gated_attention(q, out, k_pages, v_pages, block_table, batch, nq, nkv, d, dv
                     status, impl: str | None = None) -> None:
     """Attention with separate key and value sizes, an optional chunk bound and an optional output gate, by the
     kernel that fits: "mma" (bfloat16, head sizes that are multiples of 8 up to 128: flash form on the tensor
-    cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes)."""
+    cores, tiles found on the device from the step's arrays) or "generic" (32-bit arithmetic, any sizes). A step
+    with prompt portions whose keys and values are both of size 128 goes to "tcgen05": the portions' query tiles
+    to the tcgen05 flash kernel (chunk bound and gate included), the single tokens in front of them to "mma"."""
+    if impl is None and q.dtype == torch.bfloat16 and d == dv and not batch.all_decode and batch.tile_req.numel() and (
+            gate is None or (gate.stride(0) % 8 == 0 and gate.data_ptr() % 16 == 0)) and attention_prefill_tcgen05_supported(
+            nq, nkv, d, k_pages.shape[2], block_table.shape[1]):
+        impl = "tcgen05"
+    if impl == "tcgen05":
+        lead = batch.n_lead_decode
+        if lead:
+            gated_attention(q[:lead], out[:lead], k_pages, v_pages, block_table[:lead], _LeadRows(batch, lead), nq, nkv, d, dv,
+                            scale, window, chunk, gate[:lead] if gate is not None else None, status, impl="mma")
+        return attention_prefill(q, out, k_pages, v_pages, block_table, batch.q_start, batch.start_pos, batch.tile_req,
+                                 batch.tile_q0, nq, nkv, d, scale, window, status, impl="tcgen05", max_kv_len=batch.max_kv_len,
+                                 key_ranges=1 if chunk else None, chunk=chunk, gate=gate)
     if impl is None:
         impl = "mma" if q.dtype == torch.bfloat16 and gated_attention_mma_supported(nq, nkv, d, dv) and (
             gate is None or gate.stride(0) % 2 == 0) else "generic"

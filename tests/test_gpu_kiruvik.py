@@ -146,6 +146,19 @@ def test_router_choice_and_weights(E, top):
 @pytest.mark.parametrize("d, dv, H, G, chunk, window, page", [(96, 80, 6, 2, 48, 0, 64), (16, 32, 4, 1, 20, 0, 8), (128, 64, 2, 2, 0, 0, 16),
                                                              (40, 8, 6, 3, 100, 37, 32), (64, 128, 8, 2, 7, 0, 64), (24, 24, 1, 1, 0, 50, 8)])
 def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, chunk, window, page):
+    _attention_on_shuffled_pages(impl, d, dv, H, G, chunk, window, page)
+
+
+@pytest.mark.parametrize("H, G, chunk, window, page, lens", [
+    (4, 2, 48, 0, 64, [1, 1, 70, 129, 9]), (2, 1, 100, 0, 16, [1, 1, 70, 129, 9]), (3, 3, 0, 37, 32, [1, 1, 70, 129, 9]),
+    (2, 2, 300, 0, 8, [1, 1, 70, 129, 9]), (4, 1, 128, 0, 64, [70, 1, 1, 129, 9]), (2, 2, 0, 0, 128, [1, 2, 70, 129, 1])])
+def test_attention_on_tcgen05_with_chunks_and_gate(H, G, chunk, window, page, lens):
+    """Keys and values of size 128: the prompt portions' query tiles on the tcgen05 kernel with the chunk bound and
+    the gate in its epilogue, the single tokens in front of them on the mma.sync kernel, in one call."""
+    _attention_on_shuffled_pages("tcgen05", 128, 128, H, G, chunk, window, page, lens=lens)
+
+
+def _attention_on_shuffled_pages(impl, d, dv, H, G, chunk, window, page, lens=(1, 1, 70, 129, 9)):
     """Decode tokens in front of prompt portions in one launch, contexts of unequal length on pages handed out in
     random order, NaN in every page that lies wholly before what a request's rows may see (such pages go back to
     the pool while the request runs), a gate, keys and values of unequal size."""
@@ -154,7 +167,7 @@ def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, 
     from quantinfer_b200 import kernels as k
 
     torch.manual_seed(d + dv)
-    starts, lens = [130, 5, 0, 63, 200], [1, 1, 70, 129, 9]
+    starts, lens = [130, 5, 0, 63, 200], list(lens)
     B, max_blocks = len(lens), 6 * 64 // page
     n_pages = B * max_blocks
     perm = torch.randperm(n_pages)
@@ -163,7 +176,7 @@ def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, 
     table = perm.view(B, max_blocks).to(torch.int32)
     n = sum(lens)
     q = (torch.randn(n, H, d) * 1.5).to(torch.bfloat16)
-    gate = torch.randn(n, H * dv + 6).to(torch.bfloat16)
+    gate = torch.randn(n, H * dv + (8 if impl == "tcgen05" else 6)).to(torch.bfloat16)
     scale = 1.0 / math.sqrt(d)
     ref = torch.zeros(n, H, dv, dtype=torch.float64)
     lo_of = lambda p: max(p - window + 1 if window else 0, p // chunk * chunk if chunk else 0, 0)
@@ -179,13 +192,22 @@ def test_attention_kernels_on_shuffled_pages_against_float64(impl, d, dv, H, G, 
                 w = torch.softmax((keys[lo:p + 1, g] @ q[t, h].double()) * scale, dim=0)
                 ref[t, h] = (w[:, None] * vals[lo:p + 1, g]).sum(dim=0) * torch.sigmoid(gate[t, h * dv:(h + 1) * dv].double())
             t += 1
-        for b in range(lo_of(starts[e]) // page):          # pages no row of this entry sees
-            kp[table[e, b]] = float("nan")
-            vp[table[e, b]] = float("nan")
+        # pages no row of this entry sees; the tcgen05 kernel copies whole tiles of 64 keys, so it may touch (and
+        # gives weight zero to) the rows of the tile in which the first visible key lies: large numbers there, and
+        # NaN before that tile
+        unseen = lo_of(starts[e]) // page
+        before_tile = lo_of(starts[e]) // 64 * 64 // page
+        for b in range(unseen):
+            kp[table[e, b]] = vp[table[e, b]] = float("nan") if impl != "tcgen05" or b < before_tile else 100.0
     I = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    batch = SimpleNamespace(q_start=I([0] + np.cumsum(lens).tolist()), start_pos=I(starts), n_requests=B,
+    lead = next((i for i, ln in enumerate(lens) if ln > 1), B)
+    flat0 = [0] + np.cumsum(lens).tolist()
+    tiles = sorted((-(starts[e] + min(t0 + 128, lens[e])), e, flat0[e] + t0) for e in range(lead, B) for t0 in range(0, lens[e], 128))
+    batch = SimpleNamespace(q_start=I(flat0), start_pos=I(starts), n_requests=B,
                             positions=I([s0 + i for s0, ln in zip(starts, lens) for i in range(ln)]),
-                            token_req=I([e for e, ln in enumerate(lens) for _ in range(ln)]))
+                            token_req=I([e for e, ln in enumerate(lens) for _ in range(ln)]),
+                            all_decode=False, n_lead_decode=lead, max_kv_len=max(a + b for a, b in zip(starts, lens)),
+                            tile_req=I([t[1] for t in tiles]), tile_q0=I([t[2] for t in tiles]))
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     out = torch.full((n, H * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
     gd = gate.to(DEV)
@@ -269,6 +291,37 @@ def test_a_dominant_key_and_the_chunks_edges_show_in_the_mixer(tmp_path, cut, ch
     moved = ((ref - ref2).abs().max(dim=1).values > 0.05).nonzero().flatten().tolist()
     last = T - 1 if chunk is None else min(T - 1, (far // chunk + 1) * chunk - 1)
     assert moved and set(moved) <= set(range(far, last + 1)) and len(moved) >= (last - far + 1) // 2
+
+
+@pytest.mark.parametrize("cut", ["whole", "portions", "prompt then decode", "odd halves"])
+@pytest.mark.parametrize("chunk, page", [(96, 16), (64, 64), (None, 32)])
+def test_heads_of_128_in_prompt_steps_on_the_tcgen05_kernel(tmp_path, monkeypatch, cut, chunk, page):
+    """Keys and values of 128 in bfloat16: steps with portions run the framework's tcgen05 flash kernel, given the
+    chunk bound and the gate. Two inputs are scaled so that their keys dominate every row that sees them: one near
+    the end of a chunk, one at the first position of a later chunk; a bound one off moves rows by far more than
+    bfloat16 does."""
+    from quantinfer_b200 import kernels as k
+
+    entry = layer(attn(2, 1, 128, 128, 64, chunk=chunk, base=5000.0, scale=0.05), None)
+    eng, cfg, w = _one_layer(tmp_path, entry, 64, "bfloat16", page_size=page, seed=11)
+    T = 330
+    torch.manual_seed(4)
+    x = (torch.randn(T, 64) * 0.5).to(torch.bfloat16).float()
+    x[90] *= 10.0
+    x[192] *= 10.0
+    ref = plain.gated_attention(x.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    calls, inner = [], k.attention_prefill
+    monkeypatch.setattr(k, "attention_prefill", lambda *a, **kw: (calls.append(kw.get("impl")), inner(*a, **kw))[1])
+    cuts = {"odd halves": [129, 1, 127, 73]}.get(cut) or CUTS[cut](T)
+    got = _run_mixer(eng, x, cuts)
+    assert calls and set(calls) == {"tcgen05"}
+    err = (got.double() - ref).abs().max(dim=1).values
+    assert float(err.max()) < 0.05 * max(1.0, float(ref.abs().max())), (int(err.argmax()), float(err.max()))
+    x2 = x.clone()
+    x2[90] = x2[192] = 0.0
+    ref2 = plain.gated_attention(x2.double(), cfg["layers"][0]["mixer"], w, "l0.mix.")
+    moved = ((ref - ref2).abs().max(dim=1).values > 0.3).nonzero().flatten().tolist()
+    assert len(moved) >= 20
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
