@@ -344,20 +344,54 @@ extern "C" int qi_gemm_bf16(const void* x, const void* w, void* out, int out_dty
 
 // Every expert's rows through the dense tensor-core product, one launch an expert: x [pairs, K] in the experts' order,
 // w [E, N, K], y [pairs, N], all bfloat16; bounds (HOST memory) [E + 1]: expert e owns rows bounds[e] .. bounds[e + 1] - 1.
+// An expert's few hundred rows make fewer CTAs than the GPU has SMs, so the launches are dealt out over four streams
+// (the caller's and three of this library's, forked from it and joined to it by events) and run side by side; every
+// launch computes what it would alone. A stream that is being captured keeps all launches to itself.
 extern "C" int qi_moe_gemm_by_expert(const void* x, const void* w, void* y, const int* bounds, int E, int N, int K, int* status,
                                      cudaStream_t stream) {
     QI_REQUIRE(E > 0 && N > 0 && K > 0 && K % 8 == 0 && N % 8 == 0, "moe_gemm_by_expert: bad sizes E=%d N=%d K=%d", E, N, K);
-    for (int e = 0; e < E; ++e) {
+    constexpr int kSide = 3;
+    static cudaStream_t side[kSide];
+    static cudaEvent_t fork_ev, join_ev[kSide];
+    static int side_state = 0;      // 0: not made yet, 1: ready, -1: could not be made (one stream then)
+    cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess) capturing = cudaStreamCaptureStatusActive;
+    if (side_state == 0) {
+        bool ok = cudaEventCreateWithFlags(&fork_ev, cudaEventDisableTiming) == cudaSuccess;
+        for (int i = 0; i < kSide && ok; ++i)
+            ok = cudaStreamCreateWithFlags(&side[i], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&join_ev[i], cudaEventDisableTiming) == cudaSuccess;
+        side_state = ok ? 1 : -1;
+    }
+    int busy = 0;
+    for (int e = 0; e < E; ++e) busy += bounds[e + 1] > bounds[e];
+    const bool fan = side_state == 1 && capturing == cudaStreamCaptureStatusNone && busy > 1;
+    if (fan) {
+        if (cudaEventRecord(fork_ev, stream) != cudaSuccess) return qi::fail("moe_gemm_by_expert: cannot record an event");
+        for (int i = 0; i < kSide; ++i)
+            if (cudaStreamWaitEvent(side[i], fork_ev, 0) != cudaSuccess) return qi::fail("moe_gemm_by_expert: cannot fork a stream");
+    }
+    int rc = 0, launched = 0;
+    for (int e = 0; e < E && !rc; ++e) {
         const int a = bounds[e], M = bounds[e + 1] - a;
-        QI_REQUIRE(a >= 0 && M >= 0, "moe_gemm_by_expert: the experts' bounds do not ascend");
+        if (a < 0 || M < 0) {
+            rc = qi::fail("moe_gemm_by_expert: the experts' bounds do not ascend");
+            break;
+        }
         if (M == 0) continue;
         int swap, bn, splits;
         qi_gemm_bf16_plan(M, N, K, 0, &swap, &bn, &splits);
-        const int rc = qi_gemm_bf16((const qi::bf16*)x + (size_t)a * K, (const qi::bf16*)w + (size_t)e * N * K,
-                                    (qi::bf16*)y + (size_t)a * N, qi::kBF16, M, N, K, swap, bn, 1, 0, nullptr, status, stream);
-        if (rc) return rc;
+        const int lane = fan ? launched % (kSide + 1) : 0;
+        rc = qi_gemm_bf16((const qi::bf16*)x + (size_t)a * K, (const qi::bf16*)w + (size_t)e * N * K, (qi::bf16*)y + (size_t)a * N,
+                          qi::kBF16, M, N, K, swap, bn, 1, 0, nullptr, status, lane ? side[lane - 1] : stream);
+        ++launched;
     }
-    return 0;
+    if (fan) {    // joined also after a refusal, so that nothing of the side streams outlives the call's place in the stream
+        for (int i = 0; i < kSide; ++i)
+            if (cudaEventRecord(join_ev[i], side[i]) != cudaSuccess || cudaStreamWaitEvent(stream, join_ev[i], 0) != cudaSuccess)
+                return qi::fail("moe_gemm_by_expert: cannot join a stream");
+    }
+    return rc;
 }
 
 extern "C" int qi_moe_tile_rows() { return BM; }
