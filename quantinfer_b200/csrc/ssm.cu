@@ -148,6 +148,218 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
         }
 }
 
+// The same recurrence with a thread (or two neighbours) a channel: the thread keeps its channel's column S[0 .. N) in
+// registers (two threads: alternate groups of four rows each), so a token's output is a sum inside one thread (two: one
+// exchange) and B_t, C_t come as broadcast 16-byte loads from shared memory. For entries of many tokens (the second pass over segments) and states of at most 128 rows; a
+// single decode token is better off with ssm_scan_kernel, whose warps read a slot's state in contiguous rows.
+constexpr int kColChannels = 64;      // channels of a head a block takes
+
+template <typename T, int NP, int SPLIT>
+__global__ void __launch_bounds__(kColChannels * SPLIT)
+ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ raw_dt, long long lddt,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                     float* __restrict__ state, long long state_stride, float* __restrict__ y,
+                     const int* __restrict__ q_start, const int* __restrict__ start_pos, const int* __restrict__ slot_ids,
+                     int heads, int groups, int P, int N, int write_state, int vec_ok) {
+    __shared__ __align__(16) float Bs[kBatch * NP];
+    __shared__ __align__(16) float Cs[kBatch * NP];
+    __shared__ float xs[kBatch * kColChannels];
+    __shared__ float dts[kBatch], decs[kBatch];
+    qi::pdl_wait();
+    const int h = blockIdx.x, e = blockIdx.y;
+    constexpr int kColThreads = kColChannels * SPLIT, NT = NP / SPLIT;     // NT: rows of the state a thread keeps
+    const int half = (int)threadIdx.x % SPLIT;
+    const int pb = blockIdx.z * kColChannels, p = pb + (int)threadIdx.x / SPLIT;
+    const bool valid = p < P;
+    auto row_of = [&](int k) { return ((k >> 2) * SPLIT + half) * 4 + (k & 3); };      // the k-th row this thread keeps
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    const int t0 = q_start[e], t1 = q_start[e + 1];
+    const float A = -expf(a_log[h]), bias = dt_bias[h], D = d_skip[h];
+    float* st = state + (size_t)slot_ids[e] * state_stride + ((size_t)h * P + (valid ? p : 0)) * N;
+    float S[NT];
+    const bool load = valid && start_pos[e] != 0;
+#pragma unroll
+    for (int k = 0; k < NT; ++k) S[k] = (load && row_of(k) < N) ? st[row_of(k)] : 0.f;
+    const size_t xcol = (size_t)h * P + (valid ? p : 0), boff = (size_t)inner + (size_t)g * N, coff = boff + (size_t)groups * N;
+
+    // bfloat16 rows that allow 16-byte loads: the next batch's B and C are requested (eight numbers a load, all of a
+    // thread's loads in flight together) before this batch's arithmetic and put into shared memory after it
+    constexpr bool kHalf = sizeof(T) == 2;
+    constexpr int kPf = 4 * NP / kColThreads;          // 2 matrices x kBatch rows x NP / 8 vectors over the block's threads
+    const bool vec = kHalf && vec_ok;
+    uint4 pf[kPf];
+    float pf_dt = 0.f;
+    T pf_x[kBatch / SPLIT];                            // the thread's channel at every SPLIT-th token of the next batch
+    auto fetch = [&](int tb, int nb) {
+#pragma unroll
+        for (int k = 0; k < kPf; ++k) {
+            const int v = (int)threadIdx.x + kColThreads * k;
+            const int m = v / (kBatch * (NP / 8)), rem = v % (kBatch * (NP / 8)), i = rem / (NP / 8), n = (rem % (NP / 8)) * 8;
+            pf[k] = (i < nb && n < N) ? *reinterpret_cast<const uint4*>(xbc + (size_t)(tb + i) * ldx + (m ? coff : boff) + n)
+                                      : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    auto fetch_dt = [&](int tb, int nb) {
+        if ((int)threadIdx.x < nb) pf_dt = qi::to_f32<T>(raw_dt[(size_t)(tb + threadIdx.x) * lddt + h]);
+#pragma unroll
+        for (int k = 0; k < kBatch / SPLIT; ++k) {
+            const int i = k * SPLIT + half;
+            pf_x[k] = (valid && i < nb) ? xbc[(size_t)(tb + i) * ldx + xcol] : qi::from_f32<T>(0.f);
+        }
+    };
+    if (t0 < t1) {
+        if (vec) fetch(t0, min(kBatch, t1 - t0));
+        fetch_dt(t0, min(kBatch, t1 - t0));
+    }
+    for (int tb = t0; tb < t1; tb += kBatch) {
+        const int nb = min(kBatch, t1 - tb);
+        __syncthreads();                               // the batch before has been read
+        if (vec) {
+#pragma unroll
+            for (int k = 0; k < kPf; ++k) {
+                const int v = (int)threadIdx.x + kColThreads * k;
+                const int m = v / (kBatch * (NP / 8)), rem = v % (kBatch * (NP / 8));
+                float* dst = (m ? Cs : Bs) + rem * 8;
+                const uint32_t w[4] = {pf[k].x, pf[k].y, pf[k].z, pf[k].w};
+                *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(w[0] << 16), __uint_as_float(w[0] & 0xffff0000u),
+                                                              __uint_as_float(w[1] << 16), __uint_as_float(w[1] & 0xffff0000u));
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(__uint_as_float(w[2] << 16), __uint_as_float(w[2] & 0xffff0000u),
+                                                                  __uint_as_float(w[3] << 16), __uint_as_float(w[3] & 0xffff0000u));
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < nb * NP; idx += kColThreads) {     // rows beyond N are zeros: those S stay zero
+                const int i = idx / NP, n = idx % NP;
+                const T* row = xbc + (size_t)(tb + i) * ldx;
+                Bs[idx] = n < N ? qi::to_f32<T>(row[boff + n]) : 0.f;
+                Cs[idx] = n < N ? qi::to_f32<T>(row[coff + n]) : 0.f;
+            }
+        }
+        if ((int)threadIdx.x < nb) {
+            const float dt = softplus_f(pf_dt + bias);
+            dts[threadIdx.x] = dt;
+            decs[threadIdx.x] = expf(A * dt);
+        }
+#pragma unroll
+        for (int k = 0; k < kBatch / SPLIT; ++k) xs[(k * SPLIT + half) * kColChannels + (int)threadIdx.x / SPLIT] = qi::to_f32<T>(pf_x[k]);
+        __syncthreads();
+        if (tb + kBatch < t1) {
+            if (vec) fetch(tb + kBatch, min(kBatch, t1 - tb - kBatch));
+            fetch_dt(tb + kBatch, min(kBatch, t1 - tb - kBatch));
+        }
+        for (int i = 0; i < nb; ++i) {
+            const float a = decs[i], x = xs[i * kColChannels + (int)threadIdx.x / SPLIT], dx = dts[i] * x;
+            const float4* b4 = reinterpret_cast<const float4*>(Bs + i * NP);
+            const float4* c4 = reinterpret_cast<const float4*>(Cs + i * NP);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int n = 0; n < NT; n += 4) {
+                const float4 b = b4[(n >> 2) * SPLIT + half], c = c4[(n >> 2) * SPLIT + half];
+                S[n] = fmaf(a, S[n], dx * b.x);
+                S[n + 1] = fmaf(a, S[n + 1], dx * b.y);
+                S[n + 2] = fmaf(a, S[n + 2], dx * b.z);
+                S[n + 3] = fmaf(a, S[n + 3], dx * b.w);
+                acc[0] = fmaf(S[n], c.x, acc[0]);
+                acc[1] = fmaf(S[n + 1], c.y, acc[1]);
+                acc[2] = fmaf(S[n + 2], c.z, acc[2]);
+                acc[3] = fmaf(S[n + 3], c.w, acc[3]);
+            }
+            float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+            if (SPLIT == 2) sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            if (valid && half == 0) y[(size_t)(tb + i) * inner + xcol] = sum + D * x;
+        }
+    }
+    if (!write_state || !valid) return;
+#pragma unroll
+    for (int k = 0; k < NT; ++k)
+        if (row_of(k) < N) st[row_of(k)] = S[k];
+}
+
+// The end state alone (no outputs), for the first pass over segments: within a batch of kBatch tokens the recurrence is
+// unrolled, S_end = exp(A sum_u dt_u) S_begin + sum_s exp(A sum_(u > s) dt_u) dt_s B_s x_s^T, so a state element costs one
+// multiply-add a token (the weight times x is formed once a token and channel) and one multiply a batch, instead of a
+// multiply and a multiply-add a token; C is not read. Step sizes, their sums, the decays and all sums are 32-bit.
+template <typename T, int R>
+__global__ void __launch_bounds__(kWarps * 32)
+ssm_end_state_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ raw_dt, long long lddt,
+                     const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ state,
+                     long long state_stride, const int* __restrict__ q_start, const int* __restrict__ start_pos,
+                     const int* __restrict__ slot_ids, int heads, int groups, int P, int N) {
+    extern __shared__ float sm[];
+    constexpr int kBlockCols = kWarps * kCols;
+    float* Bs = sm;                              // [kBatch][N]
+    float* xs = Bs + kBatch * N;                 // [kBatch][block's columns]
+    float* dts = xs + kBatch * kBlockCols;       // [kBatch] step sizes
+    float* ws = dts + kBatch;                    // [kBatch] a token's weight in the batch's end state, then the batch's decay
+    qi::pdl_wait();
+    const int h = blockIdx.x, e = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pb = blockIdx.z * kBlockCols, p0 = pb + warp * kCols;
+    const int g = h / (heads / groups);
+    const int inner = heads * P;
+    const int t0 = q_start[e], t1 = q_start[e + 1];
+    const float A = -expf(a_log[h]), bias = dt_bias[h];
+    float* st = state + (size_t)slot_ids[e] * state_stride + ((size_t)h * P + p0) * N;
+    float S[kCols][R];
+    const bool fresh = start_pos[e] == 0;
+#pragma unroll
+    for (int c = 0; c < kCols; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int n = lane + 32 * r;
+            S[c][r] = (!fresh && n < N && p0 + c < P) ? st[(size_t)c * N + n] : 0.f;
+        }
+    const size_t xoff = (size_t)h * P + pb, boff = (size_t)inner + (size_t)g * N;
+    for (int tb = t0; tb < t1; tb += kBatch) {
+        const int nb = min(kBatch, t1 - tb);
+        __syncthreads();
+        for (int i = warp; i < nb; i += kWarps) {
+            const T* rb = xbc + (size_t)(tb + i) * ldx + boff;
+            for (int n = lane; n < N; n += 32) Bs[i * N + n] = qi::to_f32<T>(rb[n]);
+        }
+        for (int idx = threadIdx.x; idx < nb * kBlockCols; idx += blockDim.x) {
+            const int i = idx / kBlockCols, c = idx % kBlockCols;
+            xs[idx] = pb + c < P ? qi::to_f32<T>(xbc[(size_t)(tb + i) * ldx + xoff + c]) : 0.f;
+        }
+        if ((int)threadIdx.x < nb) dts[threadIdx.x] = softplus_f(qi::to_f32<T>(raw_dt[(size_t)(tb + threadIdx.x) * lddt + h]) + bias);
+        __syncthreads();
+        if ((int)threadIdx.x <= nb) {            // thread i: the step sizes after token i; thread nb: the whole batch's
+            const int i = (int)threadIdx.x == nb ? -1 : (int)threadIdx.x;
+            float after = 0.f;
+            for (int u = nb - 1; u > i; --u) after += dts[u];
+            ws[threadIdx.x == nb ? kBatch : i] = (i < 0 ? 1.f : dts[i]) * expf(A * after);
+        }
+        __syncthreads();
+        const float whole = ws[kBatch];
+#pragma unroll
+        for (int c = 0; c < kCols; ++c)
+#pragma unroll
+            for (int r = 0; r < R; ++r) S[c][r] *= whole;
+        for (int i = 0; i < nb; ++i) {
+            const float w = ws[i];
+            float B[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const int n = lane + 32 * r;
+                B[r] = n < N ? Bs[i * N + n] : 0.f;
+            }
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) {
+                const float wx = w * xs[i * kBlockCols + warp * kCols + c];
+#pragma unroll
+                for (int r = 0; r < R; ++r) S[c][r] = fmaf(wx, B[r], S[c][r]);
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < kCols; ++c)
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int n = lane + 32 * r;
+            if (n < N && p0 + c < P) st[(size_t)c * N + n] = S[c][r];
+        }
+}
+
 // Long entries are cut into segments that run side by side (the recurrence is linear in the state):
 //   1. ssm_scan over the segments as if each began a sequence: segment k's own contribution L_k to its end state;
 //   2. ssm_chain (this kernel): per entry, in order, in_k = carry ; carry = exp(A * sum of dt over k) * carry + L_k,
@@ -254,12 +466,56 @@ extern "C" int qi_ssm_scan(const void* xbc, long long ldx, const void* raw_dt, l
         qi::launch(ssm_scan_kernel<T, RR>, grid, block, smem, stream, (const T*)xbc, ldx, (const T*)raw_dt, lddt, dt_bias,     \
                    a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N, write_state);  \
     })
+#define QI_END(RR)                                                                                                          \
+    QI_DISPATCH_DTYPE(dtype, T, {                                                                                           \
+        qi::launch(ssm_end_state_kernel<T, RR>, grid, block, sizeof(float) * ((size_t)kBatch * ((size_t)N + kWarps * kCols + 2) + 1), \
+                   stream, (const T*)xbc, ldx, (const T*)raw_dt, lddt, dt_bias, a_log, state, state_stride, q_start, start_pos,  \
+                   slot_ids, heads, groups, P, N);                                                                           \
+    })
+    if (!y && write_state) {          // the end states alone
+        if (R <= 1) QI_END(1);
+        else if (R <= 2) QI_END(2);
+        else if (R <= 4) QI_END(4);
+        else QI_END(8);
+        return qi::check_launch("ssm_end_state");
+    }
     if (R <= 1) QI_SCAN(1);
     else if (R <= 2) QI_SCAN(2);
     else if (R <= 4) QI_SCAN(4);
     else QI_SCAN(8);
 #undef QI_SCAN
+#undef QI_END
     return qi::check_launch("ssm_scan");
+}
+
+// As qi_ssm_scan with outputs, a thread a channel: for entries of many tokens and N <= 128 (qi_ssm_scan_cols_supported).
+extern "C" int qi_ssm_scan_cols_supported(int N) { return N > 0 && N <= 128; }
+
+extern "C" int qi_ssm_scan_cols(const void* xbc, long long ldx, const void* raw_dt, long long lddt, int dtype, const float* dt_bias,
+                                const float* a_log, const float* d_skip, float* state, long long state_stride, float* y,
+                                const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
+                                int groups, int P, int N, int write_state, cudaStream_t stream) {
+    QI_REQUIRE(n_entries >= 0 && heads > 0 && groups > 0 && P > 0 && qi_ssm_scan_cols_supported(N) && y, "ssm_scan_cols: bad sizes");
+    QI_REQUIRE(heads % groups == 0, "ssm_scan_cols: %d heads are not a multiple of %d groups", heads, groups);
+    QI_REQUIRE(ldx >= (long long)heads * P + 2ll * groups * N && lddt >= heads, "ssm_scan_cols: the rows are too short");
+    QI_REQUIRE(state_stride >= (long long)heads * P * N, "ssm_scan_cols: the slots of the state overlap");
+    QI_REQUIRE(n_entries <= 65535, "ssm_scan_cols: grid too large");
+    if (n_entries == 0) return 0;
+    const dim3 grid(heads, n_entries, (P + kColChannels - 1) / kColChannels);
+#define QI_COLS(NP, SPLIT)                                                                                                 \
+    QI_DISPATCH_DTYPE(dtype, T, {                                                                                          \
+        qi::launch(ssm_scan_cols_kernel<T, NP, SPLIT>, grid, dim3(kColChannels * SPLIT), 0, stream, (const T*)xbc, ldx,      \
+                   (const T*)raw_dt, lddt, dt_bias,                                                                        \
+                   a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N, write_state,    \
+                   vec_ok);                                                                                                \
+    })
+    // 16-byte loads of B and C: every row, and B's and C's place in it, a multiple of eight numbers from an aligned start
+    const int vec_ok = ((uintptr_t)xbc & 15) == 0 && ldx % 8 == 0 && N % 8 == 0 && ((long long)heads * P) % 8 == 0;
+    if (N <= 32) QI_COLS(32, 1);
+    else if (N <= 64) QI_COLS(64, 2);
+    else QI_COLS(128, 2);
+#undef QI_COLS
+    return qi::check_launch("ssm_scan_cols");
 }
 
 // seg_state float32 [segments, heads, P, N] (contiguous); state as for ssm_scan; raw_dt as for ssm_scan; seg_q_start

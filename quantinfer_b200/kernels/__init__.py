@@ -1102,12 +1102,13 @@ def bias_rope_kv(proj, bias, q_out, inv_freq, rot: int, interleaved: bool, posit
 
 
 def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, slot_ids, heads: int, groups: int, P: int, N: int,
-             write_state: bool = True) -> None:
+             write_state: bool = True, long_entries: bool = False) -> None:
     """The recurrence S_t = exp(-exp(a_log) dt_t) S_(t-1) + dt_t B_t x_t^T, y_t = S_t^T C_t + d_skip x_t with
     dt_t = softplus(raw_t + dt_bias), per head over each entry's tokens. xbc [n, heads P + 2 groups N] holds x | B | C;
     raw_dt [n, heads] may be a block of columns of wider rows; state float32 [slots, heads, P, N] (read at an entry's first
     token unless it starts its sequence, written after its last unless `write_state` is False); y float32 [n, heads P], or
-    None for a pass that wants the end states only."""
+    None for a pass that wants the end states only. `long_entries`: every entry has many tokens, so the kernel that keeps a
+    channel's column of the state in one thread is worth its start (states of at most 128 rows; others run as before)."""
     for t, name in ((xbc, "xbc"), (raw_dt, "raw_dt")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"ssm_scan: {name} must be a CUDA tensor with contiguous rows")
@@ -1126,7 +1127,8 @@ def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, 
             raise KernelError("ssm_scan: y does not fit")
     for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
         _req(t, name, torch.int32, 1)
-    _call("scan", "ssm_scan", library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
+    cols = long_entries and y is not None and bool(library().qi_ssm_scan_cols_supported(N))
+    _call("scan", "ssm_scan", library().qi_ssm_scan_cols if cols else library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
           C.c_longlong(raw_dt.stride(0)), _code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state),
           C.c_longlong(state.stride(0)), _ptr(y), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, groups,
           P, N, int(bool(write_state)), _stream())

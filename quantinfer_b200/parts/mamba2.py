@@ -116,7 +116,7 @@ class Mamba2(Part):
             kernels.ssm_chain(local, ssm_state, raw_dt, self.dt_bias, self.a_log, seg_q_start, entry_seg, batch.start_pos,
                               batch.slot_ids, longest)
             kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, local, y, seg_q_start, ones, rows,
-                             s.heads, s.groups, s.head_dim, s.state, write_state=False)
+                             s.heads, s.groups, s.head_dim, s.state, write_state=False, long_entries=True)
         g = torch.empty((n, self.inner), dtype=x.dtype, device=x.device)
         kernels.gated_group_rmsnorm(y, proj[:, :self.inner], self.gain, s.norm_eps, g, s.norm_groups)
         return self.o(g, keep_partials=True)

@@ -361,11 +361,14 @@ def test_the_recurrent_mixer_however_the_sequence_is_cut(tmp_path, cut, shape):
     assert float((ref2[40] - ref[40]).abs().max()) > 1e-3
 
 
+@pytest.mark.parametrize("shape", [(3, 8, 33, 3, 3, 1), (2, 70, 20, 1, 2, 1), (2, 16, 128, 2, 4, 2), (1, 8, 150, 1, 3, 1)])
 @pytest.mark.parametrize("cuts", [[500], [250, 250], [193, 7, 300], [40, 460]])
-def test_long_entries_run_as_segments_side_by_side(tmp_path, cuts):
+def test_long_entries_run_as_segments_side_by_side(tmp_path, cuts, shape):
     """Entries of 192 tokens and more are cut into segments of 64 that run at once, chained through their states; a
-    portion's last segment is short, and the request's state must come out as if the tokens had run in a row."""
-    entry = layer(ssm(3, 8, 33, 3, 3, 1), None)
+    portion's last segment is short, and the request's state must come out as if the tokens had run in a row. States of
+    20, 33, 128 and 150 rows (the last is beyond the kernel that keeps a channel's column in one thread), a head of more
+    channels than one block of that kernel takes."""
+    entry = layer(ssm(*shape), None)
     eng, cfg, w = _one_layer(tmp_path, entry, 24, "float32", seed=19, max_tokens=1024)
     torch.manual_seed(14)
     x = torch.randn(sum(cuts) + 30, 24)
