@@ -154,7 +154,9 @@ ssm_scan_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ 
 // single decode token is better off with ssm_scan_kernel, whose warps read a slot's state in contiguous rows.
 constexpr int kColChannels = 64;      // channels of a head a block takes
 
-template <typename T, int NP, int SPLIT>
+// kEndOnly: no outputs, the end state alone by the unrolled sum that ssm_end_state_kernel describes (y is not touched,
+// C is not read, the state is always written).
+template <typename T, int NP, int SPLIT, bool kEndOnly>
 __global__ void __launch_bounds__(kColChannels * SPLIT)
 ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restrict__ raw_dt, long long lddt,
                      const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
@@ -164,7 +166,7 @@ ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restri
     __shared__ __align__(16) float Bs[kBatch * NP];
     __shared__ __align__(16) float Cs[kBatch * NP];
     __shared__ float xs[kBatch * kColChannels];
-    __shared__ float dts[kBatch], decs[kBatch];
+    __shared__ float dts[kBatch], decs[kBatch + 1];      // kEndOnly: decs holds the tokens' weights and the batch's decay
     qi::pdl_wait();
     const int h = blockIdx.x, e = blockIdx.y;
     constexpr int kColThreads = kColChannels * SPLIT, NT = NP / SPLIT;     // NT: rows of the state a thread keeps
@@ -186,7 +188,7 @@ ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restri
     // bfloat16 rows that allow 16-byte loads: the next batch's B and C are requested (eight numbers a load, all of a
     // thread's loads in flight together) before this batch's arithmetic and put into shared memory after it
     constexpr bool kHalf = sizeof(T) == 2;
-    constexpr int kPf = 4 * NP / kColThreads;          // 2 matrices x kBatch rows x NP / 8 vectors over the block's threads
+    constexpr int kPf = (kEndOnly ? 2 : 4) * NP / kColThreads;     // 1 or 2 matrices x kBatch rows x NP / 8 vectors over the block's threads
     const bool vec = kHalf && vec_ok;
     uint4 pf[kPf];
     float pf_dt = 0.f;
@@ -232,13 +234,26 @@ ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restri
                 const int i = idx / NP, n = idx % NP;
                 const T* row = xbc + (size_t)(tb + i) * ldx;
                 Bs[idx] = n < N ? qi::to_f32<T>(row[boff + n]) : 0.f;
-                Cs[idx] = n < N ? qi::to_f32<T>(row[coff + n]) : 0.f;
+                if (!kEndOnly) Cs[idx] = n < N ? qi::to_f32<T>(row[coff + n]) : 0.f;
             }
         }
-        if ((int)threadIdx.x < nb) {
-            const float dt = softplus_f(pf_dt + bias);
-            dts[threadIdx.x] = dt;
-            decs[threadIdx.x] = expf(A * dt);
+        if (!kEndOnly) {
+            if ((int)threadIdx.x < nb) {
+                const float dt = softplus_f(pf_dt + bias);
+                dts[threadIdx.x] = dt;
+                decs[threadIdx.x] = expf(A * dt);
+            }
+        } else if (threadIdx.x < 32) {       // lane i: the step sizes from token i on, added up over the lanes behind it
+            static_assert(kBatch <= 16, "the sums below cover sixteen lanes");
+            const float dt = (int)threadIdx.x < nb ? softplus_f(pf_dt + bias) : 0.f;
+            float from = dt;
+#pragma unroll
+            for (int d = 1; d < kBatch; d *= 2) {
+                const float v = __shfl_down_sync(0xffffffffu, from, d);
+                if ((int)threadIdx.x + d < kBatch) from += v;
+            }
+            if ((int)threadIdx.x < nb) decs[threadIdx.x] = dt * expf(A * (from - dt));
+            if (threadIdx.x == 0) decs[kBatch] = expf(A * from);
         }
 #pragma unroll
         for (int k = 0; k < kBatch / SPLIT; ++k) xs[(k * SPLIT + half) * kColChannels + (int)threadIdx.x / SPLIT] = qi::to_f32<T>(pf_x[k]);
@@ -246,6 +261,24 @@ ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restri
         if (tb + kBatch < t1) {
             if (vec) fetch(tb + kBatch, min(kBatch, t1 - tb - kBatch));
             fetch_dt(tb + kBatch, min(kBatch, t1 - tb - kBatch));
+        }
+        if (kEndOnly) {
+            const float whole = decs[kBatch];
+#pragma unroll
+            for (int k = 0; k < NT; ++k) S[k] *= whole;
+            for (int i = 0; i < nb; ++i) {
+                const float wx = decs[i] * xs[i * kColChannels + (int)threadIdx.x / SPLIT];
+                const float4* b4 = reinterpret_cast<const float4*>(Bs + i * NP);
+#pragma unroll
+                for (int n = 0; n < NT; n += 4) {
+                    const float4 b = b4[(n >> 2) * SPLIT + half];
+                    S[n] = fmaf(wx, b.x, S[n]);
+                    S[n + 1] = fmaf(wx, b.y, S[n + 1]);
+                    S[n + 2] = fmaf(wx, b.z, S[n + 2]);
+                    S[n + 3] = fmaf(wx, b.w, S[n + 3]);
+                }
+            }
+            continue;
         }
         for (int i = 0; i < nb; ++i) {
             const float a = decs[i], x = xs[i * kColChannels + (int)threadIdx.x / SPLIT], dx = dts[i] * x;
@@ -269,7 +302,7 @@ ssm_scan_cols_kernel(const T* __restrict__ xbc, long long ldx, const T* __restri
             if (valid && half == 0) y[(size_t)(tb + i) * inner + xcol] = sum + D * x;
         }
     }
-    if (!write_state || !valid) return;
+    if (!(write_state || kEndOnly) || !valid) return;
 #pragma unroll
     for (int k = 0; k < NT; ++k)
         if (row_of(k) < N) st[row_of(k)] = S[k];
@@ -488,14 +521,15 @@ extern "C" int qi_ssm_scan(const void* xbc, long long ldx, const void* raw_dt, l
     return qi::check_launch("ssm_scan");
 }
 
-// As qi_ssm_scan with outputs, a thread a channel: for entries of many tokens and N <= 128 (qi_ssm_scan_cols_supported).
+// As qi_ssm_scan (y null: the end states alone), a thread or two a channel: for entries of many tokens and N <= 128 (qi_ssm_scan_cols_supported).
 extern "C" int qi_ssm_scan_cols_supported(int N) { return N > 0 && N <= 128; }
 
 extern "C" int qi_ssm_scan_cols(const void* xbc, long long ldx, const void* raw_dt, long long lddt, int dtype, const float* dt_bias,
                                 const float* a_log, const float* d_skip, float* state, long long state_stride, float* y,
                                 const int* q_start, const int* start_pos, const int* slot_ids, int n_entries, int heads,
                                 int groups, int P, int N, int write_state, cudaStream_t stream) {
-    QI_REQUIRE(n_entries >= 0 && heads > 0 && groups > 0 && P > 0 && qi_ssm_scan_cols_supported(N) && y, "ssm_scan_cols: bad sizes");
+    QI_REQUIRE(n_entries >= 0 && heads > 0 && groups > 0 && P > 0 && qi_ssm_scan_cols_supported(N), "ssm_scan_cols: bad sizes");
+    QI_REQUIRE(y || write_state, "ssm_scan_cols: neither outputs nor end states are wanted");
     QI_REQUIRE(heads % groups == 0, "ssm_scan_cols: %d heads are not a multiple of %d groups", heads, groups);
     QI_REQUIRE(ldx >= (long long)heads * P + 2ll * groups * N && lddt >= heads, "ssm_scan_cols: the rows are too short");
     QI_REQUIRE(state_stride >= (long long)heads * P * N, "ssm_scan_cols: the slots of the state overlap");
@@ -504,7 +538,11 @@ extern "C" int qi_ssm_scan_cols(const void* xbc, long long ldx, const void* raw_
     const dim3 grid(heads, n_entries, (P + kColChannels - 1) / kColChannels);
 #define QI_COLS(NP, SPLIT)                                                                                                 \
     QI_DISPATCH_DTYPE(dtype, T, {                                                                                          \
-        qi::launch(ssm_scan_cols_kernel<T, NP, SPLIT>, grid, dim3(kColChannels * SPLIT), 0, stream, (const T*)xbc, ldx,      \
+        if (y) qi::launch(ssm_scan_cols_kernel<T, NP, SPLIT, false>, grid, dim3(kColChannels * SPLIT), 0, stream, (const T*)xbc, ldx, \
+                   (const T*)raw_dt, lddt, dt_bias,                                                                        \
+                   a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N, write_state,    \
+                   vec_ok);                                                                                                \
+        else qi::launch(ssm_scan_cols_kernel<T, NP, SPLIT, true>, grid, dim3(kColChannels * SPLIT), 0, stream, (const T*)xbc, ldx, \
                    (const T*)raw_dt, lddt, dt_bias,                                                                        \
                    a_log, d_skip, state, state_stride, y, q_start, start_pos, slot_ids, heads, groups, P, N, write_state,    \
                    vec_ok);                                                                                                \

@@ -1127,7 +1127,7 @@ def ssm_scan(xbc, raw_dt, dt_bias, a_log, d_skip, state, y, q_start, start_pos, 
             raise KernelError("ssm_scan: y does not fit")
     for t, name in ((q_start, "q_start"), (start_pos, "start_pos"), (slot_ids, "slot_ids")):
         _req(t, name, torch.int32, 1)
-    cols = long_entries and y is not None and bool(library().qi_ssm_scan_cols_supported(N))
+    cols = long_entries and (y is not None or write_state) and bool(library().qi_ssm_scan_cols_supported(N))
     _call("scan", "ssm_scan", library().qi_ssm_scan_cols if cols else library().qi_ssm_scan, _ptr(xbc), C.c_longlong(xbc.stride(0)), _ptr(raw_dt),
           C.c_longlong(raw_dt.stride(0)), _code(xbc), _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state),
           C.c_longlong(state.stride(0)), _ptr(y), _ptr(q_start), _ptr(start_pos), _ptr(slot_ids), start_pos.numel(), heads, groups,

@@ -112,7 +112,7 @@ class Mamba2(Part):
             seg_q_start, entry_seg, zeros, ones, rows, longest = seg
             local = torch.empty((rows.numel(), s.heads, s.head_dim, s.state), dtype=torch.float32, device=x.device)
             kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, local, None, seg_q_start, zeros, rows,
-                             s.heads, s.groups, s.head_dim, s.state)
+                             s.heads, s.groups, s.head_dim, s.state, long_entries=True)
             kernels.ssm_chain(local, ssm_state, raw_dt, self.dt_bias, self.a_log, seg_q_start, entry_seg, batch.start_pos,
                               batch.slot_ids, longest)
             kernels.ssm_scan(xbc, raw_dt, self.dt_bias, self.a_log, self.d_skip, local, y, seg_q_start, ones, rows,
