@@ -216,6 +216,15 @@ def _attention_on_shuffled_pages(impl, d, dv, H, G, chunk, window, page, lens=(1
     assert int(status.item()) == 0
     err = (out.cpu().double().view(n, H, dv) - ref).abs()
     assert float(err.max()) < 0.03, (float(err.max()), np.unravel_index(int(err.argmax()), err.shape))
+    if impl == "tcgen05":     # the same tiles with every row's keys cut into three ranges over separate CTAs: the gate is applied by the merge
+        out3 = torch.full((n, H * dv), float("nan"), dtype=torch.bfloat16, device=DEV)
+        k.attention_prefill(q.view(n, H * d).to(DEV), out3, kp.to(DEV), vp.to(DEV), table.to(DEV), batch.q_start, batch.start_pos,
+                            batch.tile_req, batch.tile_q0, H, G, d, scale, window, status, impl="tcgen05", key_ranges=3, chunk=chunk,
+                            gate=gd[:, :H * dv])
+        assert int(status.item()) == 0
+        first = int(batch.q_start[lead].item())
+        err3 = (out3[first:].cpu().double().view(n - first, H, dv) - ref[first:]).abs()
+        assert float(err3.max()) < 0.03, float(err3.max())
 
 
 # ---------------------------------------------------------------- one mixer or feed-forward alone, in an engine of one layer
