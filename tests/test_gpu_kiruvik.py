@@ -472,6 +472,33 @@ def test_replay_family(models, name, dtype, family):
     _compare(got, _expect(models, name), name, dtype, family)
 
 
+@pytest.mark.parametrize("kind", ["recurrent only", "attention only"])
+def test_models_with_one_kind_of_mixer(tmp_path, kind):
+    """A model without any attention layer has no pages to hand out, one without any recurrent layer no state rows;
+    heads of 128 / 128 here, a head of more channels than a block of the column kernel, a mixed trace on a small pool."""
+    if kind == "recurrent only":
+        cfg = {"architecture": "Kiruvik", "vocab": 90, "width": 56, "norm": {"eps": 2e-6}, "residual_mult": 0.9,
+               "loop": {"start": 0, "stop": 2, "times": 2},
+               "layers": [layer(ssm(2, 72, 24, 1, 3, 2), dense(64)), layer(ssm(4, 8, 40, 2, 2, 1), moe(4, 2, 1.2, 24, 1.1, shared=(16, 0.9))),
+                          layer(ssm(1, 16, 8, 1, 4, 1), None)]}
+    else:
+        cfg = {"architecture": "Kiruvik", "vocab": 90, "width": 56, "norm": {"eps": 2e-6}, "residual_mult": 0.9,
+               "layers": [layer(attn(2, 1, 128, 128, 64, chunk=40), dense(64)), layer(attn(4, 4, 8, 24, 4, chunk=64), moe(4, 2, 1.2, 24, 1.1)),
+                          layer(attn(3, 1, 16, 8, 16), None)]}
+    w = draw_weights(cfg, 31)
+    folder = write_folder(tmp_path / "m", cfg, w)
+    reqs = {f"q{i}": random_tokens(n, cfg["vocab"], seed=5 * i + n) for i, n in enumerate([210, 33, 70, 1, 129])}
+    expect = plain_rows(cfg, w, reqs)
+    steps, peak = mixed_trace(reqs, seed=4, max_live=4, max_tokens=round64(210) + 192)
+    for dtype, trace, max_tokens in (("float32", whole_trace(reqs), 256), ("float32", steps, peak), ("bfloat16", steps, peak)):
+        got = run_trace_engine(folder, dtype, trace, max_tokens, 16)
+        errs = [float(np.abs(got[k].astype(np.float64) - expect[k].astype(np.float64)).max()) for k in expect]
+        if dtype == "float32":
+            assert max(errs) <= TOL_F32, max(errs)
+        else:
+            assert sum(e > 0.2 for e in errs) <= BF16_ROWS_BEYOND * len(errs), sorted(errs)[-5:]
+
+
 def test_the_cuts_agree_with_one_another_bit_for_bit_in_float32(models):
     """What a position's logits are must not depend on how its prompt was cut or on its company in the batch."""
     folder, cfg, w = models["P"]
